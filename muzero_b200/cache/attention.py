@@ -1,0 +1,150 @@
+"""Decode-step attention over the quantized cache: one fused CUDA call.
+
+Same call contract as the reference's ``mu_zero_decode_attention_forward``
+(muzero/cache/attention.py:48-295): returns ``(attn_output [B,1,H,D], None)`` for a
+single-token query, ``None`` when the caller should run its stock attention
+(multi-token query or no cache layer), and counts calls in the statistics the
+reference's benchmark reads.  Where the reference launches a QK kernel, torch
+matmuls for the residual, a concatenation, a softmax, an AV kernel and an add,
+this module makes a single C-ABI call that covers packed prefix and residual.
+"""
+from __future__ import annotations
+
+import ctypes
+from collections import defaultdict
+from typing import Optional
+
+import torch
+
+from ..kernels._cabi import DecodeArgs, MuZeroKernelError, check, dtype_code, last_error, stream_ptr
+from ..kernels.loader import load_mu_zero_cuda_extension
+
+_MU_ZERO_DECODE_STATS = defaultdict(int)
+_workspaces: dict = {}
+
+
+def reset_mu_zero_decode_stats() -> None:
+    _MU_ZERO_DECODE_STATS.clear()
+
+
+def get_mu_zero_decode_stats() -> dict[str, int]:
+    return dict(_MU_ZERO_DECODE_STATS)
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """One reusable scratch buffer per (device, stream); grows, never shrinks."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def build_decode_args(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor],
+                      out: Optional[torch.Tensor], *, splits: int = 0) -> DecodeArgs:
+    """Fills the C argument block for one decode call on ``layer``."""
+    if not query.is_cuda:
+        raise MuZeroKernelError("decode attention needs CUDA tensors; this package has no CPU path")
+    if query.dtype != layer.dtype:
+        raise MuZeroKernelError(f"query dtype {query.dtype} differs from cache dtype {layer.dtype}")
+    if query.stride(-1) != 1:
+        query = query.contiguous()
+    a = DecodeArgs()
+    a.store = layer._store_struct()
+    a.q_heads = query.shape[1]
+    a.query = query.data_ptr()
+    a.q_stride_b, a.q_stride_h = query.stride(0), query.stride(1)
+    a.scaling = float(scaling)
+    a._keepalive = [query]
+    if attention_mask is not None:
+        mask = attention_mask
+        if mask.dtype == torch.bool:
+            # the reference adds the mask tensor to the logits whatever its dtype
+            mask = mask.to(query.dtype)
+        if mask.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            mask = mask.to(torch.float32)
+        total = a.store.k_groups * a.store.group + a.store.res_len
+        if mask.dim() != 4 or mask.shape[1] != 1 or mask.shape[2] != 1 or mask.shape[-1] < total:
+            raise MuZeroKernelError(f"attention_mask must be [B,1,1,>={total}], got {tuple(mask.shape)}")
+        if mask.stride(-1) != 1:
+            mask = mask.contiguous()
+        a.mask = mask.data_ptr()
+        a.mask_dtype = dtype_code(mask.dtype)
+        a.mask_stride_b = mask.stride(0) if mask.shape[0] > 1 else 0
+        a._keepalive.append(mask)
+    a.splits = int(splits)
+    if out is not None:
+        a.out = out.data_ptr()
+        a.out_dtype = dtype_code(out.dtype)
+    lib = load_mu_zero_cuda_extension()
+    need = lib.mz_decode_workspace_bytes(ctypes.byref(a))
+    if need == 0:   # the size query validates like the call does and leaves its message behind
+        raise MuZeroKernelError(f"invalid decode-attention arguments: {last_error()}")
+    ws = _workspace(query.device, need)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a._keepalive.append(ws)
+    return a
+
+
+def decode_attention(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor] = None,
+                     *, out_dtype: Optional[torch.dtype] = None, splits: int = 0) -> torch.Tensor:
+    """[B,H,1,D] query -> [B,1,H,D] attention output over ``layer``'s prefix + residual."""
+    b, h, _, d = query.shape
+    out = torch.empty((b, 1, h, d), dtype=out_dtype or query.dtype, device=query.device)
+    args = build_decode_args(layer, query, scaling, attention_mask, out, splits=splits)
+    with torch.cuda.device(query.device):
+        check(load_mu_zero_cuda_extension().mz_decode_attention(ctypes.byref(args), stream_ptr(query.device)),
+              "mz_decode_attention")
+    return out
+
+
+def decode_attention_partial(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor] = None,
+                             *, splits: int = 0):
+    """Un-normalised (m[B,H], l[B,H], acc[B,H,D]) fp32 triple of this layer's tokens."""
+    b, h, _, d = query.shape
+    dev = query.device
+    m = torch.empty((b, h), dtype=torch.float32, device=dev)
+    l = torch.empty((b, h), dtype=torch.float32, device=dev)
+    acc = torch.empty((b, h, d), dtype=torch.float32, device=dev)
+    args = build_decode_args(layer, query, scaling, attention_mask, None, splits=splits)
+    with torch.cuda.device(dev):
+        check(load_mu_zero_cuda_extension().mz_decode_attention_partial(
+            ctypes.byref(args), m.data_ptr(), l.data_ptr(), acc.data_ptr(), stream_ptr(dev)), "mz_decode_attention_partial")
+    return m, l, acc
+
+
+def lse_merge(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Merges partial triples stacked on dim 0 ([P,B,H], [P,B,H], [P,B,H,D]) -> [B,1,H,D]."""
+    p, b, h, d = acc.shape
+    out = torch.empty((b, 1, h, d), dtype=out_dtype, device=acc.device)
+    m, l, acc = m.contiguous(), l.contiguous(), acc.contiguous()
+    with torch.cuda.device(acc.device):
+        check(load_mu_zero_cuda_extension().mz_lse_merge(m.data_ptr(), l.data_ptr(), acc.data_ptr(), p, b * h, d,
+                                                         out.data_ptr(), dtype_code(out_dtype), stream_ptr(acc.device)),
+              "mz_lse_merge")
+    return out
+
+
+def mu_zero_decode_attention_forward(module, query: torch.Tensor, attention_mask, scaling: float,
+                                     kv_cache_state: dict, *, key_chunk_groups: int = 32,
+                                     value_chunk_tokens: int = 256):
+    """Attention hook for the patched model forwards; see the module docstring."""
+    layer = kv_cache_state.get("layer")
+    if layer is None:
+        _MU_ZERO_DECODE_STATS["missing_layer"] += 1
+        return None
+    if query.shape[-2] != 1:
+        _MU_ZERO_DECODE_STATS["non_decode_query"] += 1
+        return None
+    _MU_ZERO_DECODE_STATS["calls"] += 1
+    groups = getattr(module, "num_key_value_groups", None)
+    if groups is not None and query.shape[1] != groups * layer.keys.shape[1]:
+        raise MuZeroKernelError("query heads do not match num_key_value_groups * kv heads")
+    out = decode_attention(layer, query, scaling, attention_mask)
+    if int(kv_cache_state.get("key_prefix_length", 0)) > 0:
+        _MU_ZERO_DECODE_STATS["fused_qk_success"] += 1
+        _MU_ZERO_DECODE_STATS["fused_av_success"] += 1
+        _MU_ZERO_DECODE_STATS["fused_prefix_decode_success"] += 1
+    _MU_ZERO_DECODE_STATS["returns"] += 1
+    return out, None

@@ -1,0 +1,160 @@
+// Decode attention entry points: argument checks, split selection, workspace carving,
+// kernel dispatch, and the deterministic log-sum-exp combine.
+#include "mz_decode.cuh"
+
+namespace {
+
+// out[row, :] = sum_p acc[p,row,:] * exp(m[p,row] - m*) (/ sum_p l[p,row] * exp(m[p,row] - m*) when normalising)
+__global__ void lse_combine_kernel(const float* __restrict__ m, const float* __restrict__ l, const float* __restrict__ acc,
+                                   int n_parts, long long row_stride, long long part_stride, int D,
+                                   void* __restrict__ out, int out_dt, float* __restrict__ out_m, float* __restrict__ out_l,
+                                   float* __restrict__ out_acc) {
+  const long long row = blockIdx.x;
+  float mx = -INFINITY;
+  for (int p = 0; p < n_parts; ++p) mx = fmaxf(mx, m[row * row_stride + p * part_stride]);
+  float lsum = 0.f;
+  for (int p = 0; p < n_parts; ++p) {
+    const long long i = row * row_stride + p * part_stride;
+    const float w = (m[i] > -INFINITY) ? __expf(m[i] - mx) : 0.f;
+    lsum += l[i] * w;
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float a = 0.f;
+    for (int p = 0; p < n_parts; ++p) {
+      const long long i = row * row_stride + p * part_stride;
+      const float w = (m[i] > -INFINITY) ? __expf(m[i] - mx) : 0.f;
+      a = fmaf(acc[i * D + d], w, a);
+    }
+    if (out) mz_store_from_float(out, row * D + d, a / fmaxf(lsum, 1e-20f), out_dt);
+    else out_acc[row * D + d] = a;
+  }
+  if (!out && threadIdx.x == 0) { out_m[row] = mx; out_l[row] = lsum; }
+}
+
+int g_sm_count = 0;
+int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+struct Plan {
+  MzDecodeParams p;
+  bool tiles;
+  int units;
+  size_t ws_bytes;
+};
+
+int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
+  MZ_REQUIRE(a != nullptr, "args is NULL");
+  const mz_kv_store* s = &a->store;
+  int rc = mz_check_store_basic(s);
+  if (rc) return rc;
+  MZ_REQUIRE(a->q_heads > 0 && a->q_heads % s->kv_heads == 0, "q_heads %d is not a multiple of kv_heads %d", a->q_heads, s->kv_heads);
+  MZ_REQUIRE(s->k_groups * s->group == s->v_tokens, "key prefix (%d tokens) and value prefix (%d tokens) differ", s->k_groups * s->group,
+             s->v_tokens);
+  MZ_REQUIRE(s->k_groups > 0 || s->res_len > 0, "no tokens to attend to");
+  if (s->k_groups > 0 && (rc = mz_check_store_quantized(s))) return rc;
+  if (s->res_len > 0 && (rc = mz_check_store_residual(s))) return rc;
+  MZ_REQUIRE(a->query != nullptr, "query is NULL");
+  MZ_REQUIRE(a->mask == nullptr || mz_dtype_ok(a->mask_dtype), "bad mask dtype");
+  MZ_REQUIRE(a->splits >= 0, "splits must be >= 0");
+  MzDecodeParams& p = plan->p;
+  p.s = *s;
+  p.H = a->q_heads;
+  p.gqa = a->q_heads / s->kv_heads;
+  p.query = a->query; p.q_stride_b = a->q_stride_b; p.q_stride_h = a->q_stride_h;
+  p.scaling = a->scaling;
+  p.mask = a->mask; p.mask_dtype = a->mask_dtype; p.mask_stride_b = a->mask_stride_b;
+  p.QB = mz_row_bytes(s->group, s->bits);
+  p.NG = (s->head_dim + s->group - 1) / s->group;
+  p.eps = 1e-8f;
+  p.table_k = p.table_v = nullptr;
+  plan->tiles = mz_decode_tiles_supported(p);
+  plan->units = plan->tiles ? mz_decode_units_tiles(*s) : mz_decode_units_generic(*s);
+  int splits = a->splits;
+  if (splits == 0) {
+    // aim for about two waves of CTAs over the SMs, but at least 4 units per CTA
+    const long long pairs = (long long)s->batch * s->kv_heads;
+    const long long want = (2LL * sm_count() * (plan->tiles ? 2 : 4) + pairs - 1) / pairs;
+    splits = (int)want;
+    if (splits > plan->units / 4) splits = plan->units / 4;
+    if (splits < 1) splits = 1;
+  }
+  if (splits > plan->units) splits = plan->units;
+  p.splits = splits;
+  const size_t slots = (size_t)s->batch * a->q_heads * splits;
+  plan->ws_bytes = slots * sizeof(float) * (2 + (size_t)s->head_dim);
+  if (need_tables && !plan->tiles) {
+    if ((rc = mz_get_expand_table(s->bits, s->alpha_key, &p.table_k))) return rc;
+    if ((rc = mz_get_expand_table(s->bits, s->alpha_value, &p.table_v))) return rc;
+  }
+  return MZ_OK;
+}
+
+int run_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
+  int rc = make_plan(a, plan, true);
+  if (rc) return rc;
+  if (a->workspace == nullptr || a->workspace_bytes < plan->ws_bytes)
+    return mz_fail(MZ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", plan->ws_bytes, a->workspace_bytes);
+  MZ_REQUIRE((uintptr_t)a->workspace % 16 == 0, "workspace must be 16-byte aligned");
+  MzDecodeParams& p = plan->p;
+  const size_t slots = (size_t)p.s.batch * p.H * p.splits;
+  p.part.m = (float*)a->workspace;
+  p.part.l = p.part.m + slots;
+  p.part.acc = p.part.l + slots;
+  return plan->tiles ? mz_launch_decode_tiles(p, st) : mz_launch_decode_generic(p, st);
+}
+}  // namespace
+
+extern "C" size_t mz_decode_workspace_bytes(const mz_decode_args* args) {
+  Plan plan;
+  if (make_plan(args, &plan, false) != MZ_OK) return 0;
+  return plan.ws_bytes;
+}
+
+extern "C" int mz_decode_attention(const mz_decode_args* a, void* stream) {
+  Plan plan;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = run_partials(a, &plan, st);
+  if (rc) return rc;
+  MZ_REQUIRE(a->out != nullptr && mz_dtype_ok(a->out_dtype), "bad output");
+  const MzDecodeParams& p = plan.p;
+  const int D = p.s.head_dim;
+  const int threads = D >= 128 ? 128 : ((D + 31) / 32) * 32;
+  lse_combine_kernel<<<(unsigned)(p.s.batch * p.H), threads, 0, st>>>(p.part.m, p.part.l, p.part.acc, p.splits, p.splits, 1, D, a->out,
+                                                                      a->out_dtype, nullptr, nullptr, nullptr);
+  MZ_LAUNCH_CHECK("lse_combine");
+  return MZ_OK;
+}
+
+extern "C" int mz_decode_attention_partial(const mz_decode_args* a, float* m, float* l, float* acc, void* stream) {
+  Plan plan;
+  cudaStream_t st = (cudaStream_t)stream;
+  MZ_REQUIRE(m && l && acc, "NULL partial output");
+  int rc = run_partials(a, &plan, st);
+  if (rc) return rc;
+  const MzDecodeParams& p = plan.p;
+  const int D = p.s.head_dim;
+  const int threads = D >= 128 ? 128 : ((D + 31) / 32) * 32;
+  lse_combine_kernel<<<(unsigned)(p.s.batch * p.H), threads, 0, st>>>(p.part.m, p.part.l, p.part.acc, p.splits, p.splits, 1, D, nullptr,
+                                                                      MZ_F32, m, l, acc);
+  MZ_LAUNCH_CHECK("lse_combine_partial");
+  return MZ_OK;
+}
+
+extern "C" int mz_lse_merge(const float* m, const float* l, const float* acc, int n_parts, long long rows, int head_dim, void* out,
+                            int out_dtype, void* stream) {
+  MZ_REQUIRE(m && l && acc && out, "NULL pointer");
+  MZ_REQUIRE(n_parts > 0 && rows > 0 && head_dim > 0, "bad shape");
+  MZ_REQUIRE(mz_dtype_ok(out_dtype), "bad out_dtype");
+  MZ_REQUIRE(rows < (1LL << 31), "too many rows");
+  const int threads = head_dim >= 128 ? 128 : ((head_dim + 31) / 32) * 32;
+  lse_combine_kernel<<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(m, l, acc, n_parts, 1, rows, head_dim, out, out_dtype, nullptr,
+                                                                           nullptr, nullptr);
+  MZ_LAUNCH_CHECK("lse_merge");
+  return MZ_OK;
+}

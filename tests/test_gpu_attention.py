@@ -1,0 +1,176 @@
+"""GPU: fused decode attention through the C-ABI against the reference's fp32 evaluation
+(golden) and the oracle.  Tolerance: max-abs 2e-3 on fp32 output; bf16 output adds half a
+bf16 ulp of the value (the rounding of the output itself)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits16, from_bits16, sha
+from test_gpu_layer import CASES, gpu_layer_from_meta
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def bf16_half_ulp(x: torch.Tensor) -> torch.Tensor:
+    e = torch.floor(torch.log2(x.abs().clamp_min(1e-30)))
+    return torch.pow(2.0, e - 8)
+
+
+def check_output(out_f32, out_bf16, ref):
+    assert out_f32.shape == ref.shape
+    err = (out_f32.cpu() - ref).abs().max().item()
+    assert err <= TOL, f"fp32 output max-abs error {err}"
+    slack = TOL + bf16_half_ulp(ref)
+    assert bool(((out_bf16.float().cpu() - ref).abs() <= slack).all())
+    return err
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_attention_golden_cases(oracle, golden, name):
+    from muzero_b200.cache.attention import decode_attention
+    meta = golden.layer_meta[name]
+    layer, q = gpu_layer_from_meta(oracle, meta)
+    ref = torch.from_numpy(golden.layer[name + "/attn_fp32"])
+    scaling = meta["D"] ** -0.5
+    o32 = decode_attention(layer, q, scaling, out_dtype=torch.float32)
+    obf = decode_attention(layer, q, scaling)
+    check_output(o32, obf, ref)
+    # split count must not matter beyond fp32 summation order; results are deterministic
+    for splits in (1, 2, 5, 64):
+        o = decode_attention(layer, q, scaling, out_dtype=torch.float32, splits=splits)
+        assert (o - o32).abs().max().item() < 2e-5
+    again = decode_attention(layer, q, scaling, out_dtype=torch.float32)
+    assert torch.equal(again, o32)
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_config0_full(oracle, golden, bits):
+    """BASELINE config 0: codes/metadata bit-exact (sha256 of the reference's tensors), attention within 2e-3."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
+    k, v, q = oracle.synth_kv(1, 8, 4096, 128, 32, seed=0)
+    m = golden.config0_meta[f"b{bits}"]
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=64, residual_length=128))
+    layer.update(k.cuda(), v.cuda(), {"materialize_full_kv": False})
+    assert sha(layer._packed_key_q) == m["packed_k"] and sha(layer._packed_value_q) == m["packed_v"]
+    assert sha(layer._key_mn) == m["k_mn"] and sha(layer._key_scale) == m["k_scale"]
+    assert sha(layer._value_mn) == m["v_mn"] and sha(layer._value_scale) == m["v_scale"]
+    assert sha(layer._dequantize_key_prefix()) == m["deq_k_bf16"]
+    assert sha(layer._dequantize_value_prefix()) == m["deq_v_bf16"]
+    ref = torch.from_numpy(golden.config0[f"b{bits}_attn_fp32"])
+    o32 = decode_attention(layer, q.cuda(), 128 ** -0.5, out_dtype=torch.float32)
+    obf = decode_attention(layer, q.cuda(), 128 ** -0.5)
+    check_output(o32, obf, ref)
+
+
+def _oracle_and_gpu_layers(oracle, B, KVH, H, S, D, bits, group, residual, seed, steps=0):
+    import muzero_b200 as mz
+    k, v, q = oracle.synth_kv(B, KVH, S + steps, D, H, seed=seed)
+    ref = oracle.OracleCacheLayer(bits=bits, group=group, residual=residual)
+    cfg = mz.MuZeroConfig(bits=4, q_group_size=group, residual_length=residual)
+    cfg.bits = bits     # 5 and 6 bits are outside the config's list but inside the kernels' range
+    layer = mz.MuZeroCacheLayer(cfg)
+    ref.append(k[:, :, :S].contiguous(), v[:, :, :S].contiguous())
+    layer.update(k[:, :, :S].cuda().contiguous(), v[:, :, :S].cuda().contiguous(), {"materialize_full_kv": False})
+    for i in range(S, S + steps):
+        ref.append(k[:, :, i:i + 1].contiguous(), v[:, :, i:i + 1].contiguous())
+        layer.update(k[:, :, i:i + 1].cuda(), v[:, :, i:i + 1].cuda(), {"materialize_full_kv": False})
+    return ref, layer, q
+
+
+@pytest.mark.parametrize("bits,group", [(1, 32), (3, 128), (5, 32), (5, 128), (6, 64), (7, 32), (8, 128), (4, 32), (2, 128), (1, 128), (8, 32)])
+def test_any_bits_and_groups_vs_oracle(oracle, bits, group):
+    from muzero_b200.cache.attention import decode_attention
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 2, 2, 8, 700, 128, bits, group, 128, seed=bits * 10 + group, steps=3)
+    want = oracle.decode_attention_oracle(q, ref, 128 ** -0.5, 4, compute_dtype=torch.float32)
+    o32 = decode_attention(layer, q.cuda(), 128 ** -0.5, out_dtype=torch.float32)
+    obf = decode_attention(layer, q.cuda(), 128 ** -0.5)
+    check_output(o32, obf, want)
+
+
+@pytest.mark.parametrize("gqa,D", [(1, 128), (2, 128), (8, 128), (4, 64), (4, 16), (3, 96)])
+def test_head_shapes(oracle, gqa, D):
+    from muzero_b200.cache.attention import decode_attention
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 2, 2, 2 * gqa, 333, D, 4, 64, 64, seed=gqa * 100 + D, steps=70)
+    want = oracle.decode_attention_oracle(q, ref, D ** -0.5, gqa, compute_dtype=torch.float32)
+    o32 = decode_attention(layer, q.cuda(), D ** -0.5, out_dtype=torch.float32)
+    check_output(o32, decode_attention(layer, q.cuda(), D ** -0.5), want)
+
+
+def test_residual_only_and_additive_mask(oracle):
+    from muzero_b200.cache.attention import decode_attention
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 2, 2, 8, 100, 128, 4, 64, 128, seed=77)
+    assert layer._packed_key_q is None
+    want = oracle.decode_attention_oracle(q, ref, 0.1, 4, compute_dtype=torch.float32)
+    check_output(decode_attention(layer, q.cuda(), 0.1, out_dtype=torch.float32), decode_attention(layer, q.cuda(), 0.1), want)
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 2, 2, 8, 500, 128, 4, 64, 128, seed=78, steps=5)
+    total = 505
+    mask = torch.zeros(2, 1, 1, total + 3)
+    mask[0, ..., :37] = torch.finfo(torch.bfloat16).min      # left padding of sequence 0
+    mask[1, ..., 400:450] = -5.0
+    want = oracle.decode_attention_oracle(q, ref, 0.09, 4, mask=mask, compute_dtype=torch.float32)
+    for mdt in (torch.float32, torch.bfloat16):
+        got = decode_attention(layer, q.cuda(), 0.09, mask.to(mdt).cuda(), out_dtype=torch.float32)
+        assert (got.cpu() - want).abs().max().item() <= TOL
+
+
+def test_partials_merge_like_a_kv_split(oracle):
+    """Two stores holding the two halves of one sequence: merged partial triples equal the one-store result."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention, decode_attention_partial, lse_merge
+    k, v, q = oracle.synth_kv(2, 2, 1024, 128, 8, seed=91)
+    whole = mz.MuZeroCacheLayer(mz.MuZeroConfig(residual_length=0))
+    whole.update(k.cuda(), v.cuda(), {"materialize_full_kv": False})
+    a = mz.MuZeroCacheLayer(mz.MuZeroConfig(residual_length=0))
+    a.update(k[:, :, :512].cuda().contiguous(), v[:, :, :512].cuda().contiguous(), {"materialize_full_kv": False})
+    b = mz.MuZeroCacheLayer(mz.MuZeroConfig(residual_length=0))
+    b.update(k[:, :, 512:].cuda().contiguous(), v[:, :, 512:].cuda().contiguous(), {"materialize_full_kv": False})
+    qc = q.cuda()
+    pa, pb = decode_attention_partial(a, qc, 0.088), decode_attention_partial(b, qc, 0.088)
+    merged = lse_merge(torch.stack([pa[0], pb[0]]), torch.stack([pa[1], pb[1]]), torch.stack([pa[2], pb[2]]), torch.float32)
+    one = decode_attention(whole, qc, 0.088, out_dtype=torch.float32)
+    assert (merged - one).abs().max().item() < 2e-5
+    m, l, acc = (t.cpu() for t in pa)
+    om, ol, oacc = oracle.attention_partial_oracle(q, _dense(oracle, a, "k"), _dense(oracle, a, "v"), 0.088, 4)
+    assert (m - om).abs().max().item() < 1e-3
+    assert ((acc / l.unsqueeze(-1)) - (oacc / ol.unsqueeze(-1))).abs().max().item() < TOL
+
+
+def _dense(oracle, layer, which):
+    return (layer._dequantize_key_prefix() if which == "k" else layer._dequantize_value_prefix()).float().cpu()
+
+
+def test_two_kernel_api_qk_and_av(oracle):
+    """mu_zero_qk_cuda / mu_zero_av_cuda with the reference's argument order."""
+    from muzero_b200.kernels import mu_zero_qk_cuda, mu_zero_av_cuda
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 2, 2, 8, 448, 128, 4, 64, 64, seed=12)
+    qc = q.cuda()
+    S = layer._packed_key_q.shape[2] * 64
+    logits = torch.empty(2, 8, S, dtype=torch.float32, device="cuda")
+    mu_zero_qk_cuda(qc, layer._packed_key_q.contiguous(), layer._key_mn.contiguous(), layer._key_scale.contiguous(), logits,
+                    4, 2.0, 4, 0.088)
+    kd = ref.key_prefix(torch.float32).repeat_interleave(4, dim=1)
+    want = torch.einsum("bhd,bhsd->bhs", q.float().squeeze(2), kd) * 0.088
+    assert (logits.cpu() - want).abs().max().item() < 1e-3
+    w = torch.softmax(want, dim=-1).cuda()
+    out = torch.empty(2, 8, 128, dtype=torch.float32, device="cuda")
+    mu_zero_av_cuda(w, layer._packed_value_q.contiguous(), layer._value_mn.contiguous(), layer._value_scale.contiguous(), out,
+                    4, 2.0, 4, 64)
+    vd = ref.value_prefix(torch.float32).repeat_interleave(4, dim=1)
+    assert (out.cpu() - torch.einsum("bhs,bhsd->bhd", w.cpu(), vd)).abs().max().item() < 1e-4
+
+
+def test_hook_contract_and_stats(oracle):
+    from types import SimpleNamespace
+    import muzero_b200 as mz
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 1, 2, 8, 300, 128, 4, 64, 128, seed=3)
+    mz.reset_mu_zero_decode_stats()
+    mod = SimpleNamespace(num_key_value_groups=4)
+    out, w = mz.mu_zero_decode_attention_forward(mod, q.cuda(), None, 0.088, layer.get_attention_state())
+    assert w is None and out.shape == (1, 1, 8, 128) and out.dtype == torch.bfloat16 and out.is_contiguous()
+    assert mz.mu_zero_decode_attention_forward(mod, torch.cat([q, q], dim=2).cuda(), None, 0.088, layer.get_attention_state()) is None
+    assert mz.mu_zero_decode_attention_forward(mod, q.cuda(), None, 0.088, {}) is None
+    st = mz.get_mu_zero_decode_stats()
+    assert st["calls"] == 1 and st["returns"] == 1 and st["fused_qk_success"] == 1 and st["fused_av_success"] == 1
+    assert st["non_decode_query"] == 1 and st["missing_layer"] == 1

@@ -1,0 +1,145 @@
+"""GPU: MuZeroCacheLayer (flush, append, store layout, dequantization) against golden states and the oracle layer."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits16, sha
+from test_oracle_golden import build_case
+
+pytestmark = pytest.mark.gpu
+CASES = ["c4g64", "c2g64", "c3g32", "c8g128", "c1g64", "c7g64", "c4g64_d64", "c4g64_dec", "c2g64_dec4g",
+         "c4g64_bf16meta", "c4g64_f32meta"]
+
+
+def _meta_arr(t):
+    t = t.detach().cpu().contiguous()
+    return t.numpy() if t.dtype == torch.float32 else bits16(t)
+
+
+def gpu_layer_from_meta(oracle, meta, hf_strides=False):
+    import muzero_b200 as mz
+    extra = dict(meta["extra"])
+    cfg = mz.MuZeroConfig(bits=meta["bits"], q_group_size=meta["group"], residual_length=meta["residual"], **extra)
+    layer = mz.MuZeroCacheLayer(cfg)
+    k, v, q = oracle.synth_kv(meta["B"], meta["KVH"], meta["S"] + meta["steps"], meta["D"], meta["H"], seed=meta["seed"])
+    S = meta["S"]
+    kc, vc = k[:, :, :S].cuda(), v[:, :, :S].cuda()
+    if hf_strides:   # the layout a model hands over: [B,S,KVH,D] transposed to [B,KVH,S,D]
+        kc = kc.transpose(1, 2).contiguous().transpose(1, 2)
+        vc = vc.transpose(1, 2).contiguous().transpose(1, 2)
+    else:
+        kc, vc = kc.contiguous(), vc.contiguous()
+    layer.update(kc, vc, {"materialize_full_kv": False})
+    for i in range(meta["steps"]):
+        layer.update(k[:, :, S + i:S + i + 1].cuda(), v[:, :, S + i:S + i + 1].cuda(), {"materialize_full_kv": False})
+    return layer, q.cuda()
+
+
+@pytest.mark.parametrize("hf_strides", [False, True])
+@pytest.mark.parametrize("name", CASES)
+def test_layer_state_matches_reference(oracle, golden, name, hf_strides):
+    meta = golden.layer_meta[name]
+    layer, _ = gpu_layer_from_meta(oracle, meta, hf_strides)
+    g = golden.layer
+    assert np.array_equal(layer._packed_key_q.cpu().numpy(), g[name + "/packed_k"])
+    assert np.array_equal(layer._packed_value_q.cpu().numpy(), g[name + "/packed_v"])
+    for attr, nm in (("_key_mn", "k_mn"), ("_key_scale", "k_scale"), ("_value_mn", "v_mn"), ("_value_scale", "v_scale")):
+        assert np.array_equal(_meta_arr(getattr(layer, attr)), g[f"{name}/{nm}"]), nm
+    assert np.array_equal(bits16(layer.keys), g[name + "/res_k"])
+    assert np.array_equal(bits16(layer.values), g[name + "/res_v"])
+    assert [layer._selected_alpha_key, layer._selected_alpha_value] == list(g[name + "/alpha"])
+    assert sha(layer._dequantize_key_prefix()) == meta["deq_bf16_sha"]["k"]
+    assert sha(layer._dequantize_value_prefix()) == meta["deq_bf16_sha"]["v"]
+    state = layer.get_attention_state()
+    assert state["key_prefix_length"] == g[name + "/packed_k"].shape[2] * meta["group"] == state["value_prefix_length"]
+
+
+def test_step_by_step_against_oracle_layer(oracle):
+    """Prefill + 200 single-token updates: store, residual and lengths equal the oracle's after every step."""
+    import muzero_b200 as mz
+    k, v, _ = oracle.synth_kv(2, 2, 150 + 200, 128, 4, seed=21)
+    ref = oracle.OracleCacheLayer(bits=4, group=32, residual=64)
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=4, q_group_size=32, residual_length=64))
+    ref.append(k[:, :, :150].contiguous(), v[:, :, :150].contiguous())
+    layer.update(k[:, :, :150].cuda().contiguous(), v[:, :, :150].cuda().contiguous(), {"materialize_full_kv": False})
+    for i in range(150, 350):
+        ref.append(k[:, :, i:i + 1].contiguous(), v[:, :, i:i + 1].contiguous())
+        rk, rv = layer.update(k[:, :, i:i + 1].cuda(), v[:, :, i:i + 1].cuda(), {"materialize_full_kv": False})
+        assert rk.shape[2] == ref.keys.shape[2] and layer.get_seq_length() == i + 1
+        if i % 16 == 0 or i == 349:
+            assert torch.equal(layer._packed_key_q.cpu(), ref.packed_k)
+            assert torch.equal(layer._packed_value_q.cpu(), ref.packed_v)
+            assert np.array_equal(bits16(layer._key_scale), bits16(ref.k_scale))
+            assert np.array_equal(bits16(layer.keys), bits16(ref.keys))
+            assert np.array_equal(bits16(layer.values), bits16(ref.values))
+
+
+def test_range_dequant_and_full_materialisation(oracle):
+    import muzero_b200 as mz
+    k, v, _ = oracle.synth_kv(1, 2, 512, 128, 4, seed=33)
+    ref = oracle.OracleCacheLayer(bits=4, group=64, residual=128)
+    ref.append(k, v)
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig())
+    layer.update(k.cuda(), v.cuda())
+    kp, vp = ref.key_prefix(torch.bfloat16), ref.value_prefix(torch.bfloat16)
+    assert np.array_equal(bits16(layer._dequantize_key_range(1, 4)), bits16(kp[:, :, 64:256].contiguous()))
+    assert np.array_equal(bits16(layer._dequantize_value_range(100, 300)), bits16(vp[:, :, 100:300].contiguous()))
+    k1, v1, _ = oracle.synth_kv(1, 2, 1, 128, 4, seed=34)
+    fk, fv = layer.update(k1.cuda(), v1.cuda())       # default: full dense K/V
+    assert fk.shape[2] == 513
+    want = torch.cat([kp, ref.keys, k1], dim=2)
+    assert np.array_equal(bits16(fk), bits16(want))
+
+
+def test_reference_cache_suite():
+    """The reference's own unit tests for the layer (tests/test_cache.py), on the CUDA path."""
+    import muzero_b200 as mz
+
+    def make(**kw):
+        base = dict(bits=4, q_group_size=64, residual_length=128)
+        base.update(kw)
+        return mz.MuZeroCacheLayer(mz.MuZeroConfig(**base))
+
+    def kv(bs, nh, sl, hd):
+        return (torch.randn(bs, nh, sl, hd, device="cuda", dtype=torch.float16),
+                torch.randn(bs, nh, sl, hd, device="cuda", dtype=torch.float16))
+
+    layer = make()
+    k, v = kv(1, 8, 512, 128)
+    rk, rv = layer.update(k, v, {"materialize_full_kv": True})
+    assert rk.shape == k.shape and rv.shape == v.shape
+    assert layer._packed_key_q is not None and layer._packed_value_q is not None
+    small = make()
+    small.update(*kv(1, 8, 64, 128))
+    assert small._packed_key_q is None
+    k2, v2 = kv(1, 8, 1, 128)
+    assert layer.update(k2, v2)[0].shape[-2] == 513 and layer.get_seq_length() == 513
+    assert layer.update(*kv(1, 8, 1, 128), {"materialize_full_kv": False})[0].shape[-2] <= 129 + 64
+    by_group = make(decode_flush_by_group=True)
+    by_group.update(*kv(1, 8, 128, 128))
+    assert by_group._packed_key_q is None
+    for _ in range(64):
+        by_group.update(*kv(1, 8, 1, 128), {"materialize_full_kv": False})
+    assert by_group._packed_key_q.shape[2] == 1 and by_group._packed_value_q.shape[2] == 64
+    assert by_group.keys.shape[2] == 128 and by_group.values.shape[2] == 128
+    layer.reset()
+    assert not layer.is_initialized and layer._packed_key_q is None and layer.cumulative_length == 0
+    for bits in (2, 4, 8):
+        l2 = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=64, residual_length=64))
+        k, v = kv(1, 4, 256, 64)
+        assert l2.update(k, v, {"materialize_full_kv": True})[0].shape == k.shape
+
+
+def test_crop_reorder_offload(oracle):
+    import muzero_b200 as mz
+    k, v, _ = oracle.synth_kv(3, 2, 400, 128, 4, seed=5)
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig())
+    layer.update(k.cuda(), v.cuda())
+    full_k, _ = layer._full_kv()
+    layer.batch_select_indices(torch.tensor([2, 0], device="cuda"))
+    sel_k, _ = layer._full_kv()
+    assert torch.equal(sel_k, full_k[[2, 0]])
+    layer.offload(); layer.prefetch()
+    assert torch.equal(layer._full_kv()[0], full_k[[2, 0]])
+    layer.crop(100)
+    assert layer.get_seq_length() == 100 and torch.equal(layer.keys, full_k[[2, 0], :, :100])
