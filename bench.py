@@ -1,0 +1,334 @@
+"""Benchmark of the KV-cache hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE config 1 shape, one decode step of the hot path for a Qwen3-8B shaped
+model): per GPU 36 layers, each a quantized cache of batch 64 x 8 kv heads x (4096 packed +
+128 residual) tokens x head_dim 128, 32 query heads, 4-bit codes, group 64, fp16 metadata.
+A step is, for every layer: append the new K/V token, flush the residual window when due,
+and run the fused decode attention.  36 distinct layer caches (17 GB) are walked per step, so
+every read comes from HBM, not L2.  Synthetic K/V: V~N(0,1), K~N(0,1) with log-normal channel
+scales, q~N(0,1), seeded.
+
+  value     tokens/s through the C ABI with all inputs resident in HBM
+  e2e       tokens/s through the plug-in API (MuZeroCache.update + mu_zero_decode_attention_forward)
+            with pinned host q/k/v copied in and the attention output copied out every step
+  roofline  algorithmic bytes of one decode-attention call / its mean duration (CUDA events on
+            the launch stream, timed region only) against the measured HBM copy bandwidth
+  cpu_baseline / --impl reference
+            the CPU restatement of the reference's PyTorch path (oracle/) on the host cores,
+            on a bounded sample of the same workload
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS, BATCH, KVH, QH, CTX, RES, D, GROUP = 36, 64, 8, 32, 4096, 128, 128, 64
+
+
+def algorithmic_bytes(bits: int, batch=BATCH, sq=CTX, res=RES, meta=2, elem=2) -> int:
+    """Bytes one decode-attention call must move: packed codes + metadata + residual + q/out."""
+    per_pair = 2 * sq * D * bits // 8 + (sq // GROUP) * D * 2 * meta + sq * (D // GROUP) * 2 * meta + 2 * res * D * elem
+    return batch * KVH * per_pair + 2 * batch * QH * D * elem
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_layers(bits: int, device: torch.device, layers: int, batch: int, seed: int):
+    """`layers` caches holding CTX quantized + RES residual tokens each (values drawn on the device)."""
+    import muzero_b200 as mz
+    gen = torch.Generator(device=device).manual_seed(seed)
+    chan = torch.exp(torch.randn(D, device=device, generator=gen))
+    out = []
+    for _ in range(layers):
+        layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=GROUP, residual_length=RES))
+        layer.max_cache_length = CTX + RES + 1024
+        k = (torch.randn(batch, KVH, CTX + RES, D, device=device, generator=gen) * chan).to(torch.bfloat16)
+        v = torch.randn(batch, KVH, CTX + RES, D, device=device, generator=gen).to(torch.bfloat16)
+        layer.update(k, v, {"materialize_full_kv": False})
+        del k, v
+        out.append(layer)
+    return out
+
+
+class CabiSession:
+    """Drives the C ABI directly: per layer one append, a flush when due, one fused attention."""
+
+    def __init__(self, layers, q, k_new, v_new):
+        from muzero_b200.cache.attention import build_decode_args
+        from muzero_b200.kernels.loader import load_mu_zero_cuda_extension
+        from muzero_b200.kernels._cabi import stream_ptr
+        self.lib = load_mu_zero_cuda_extension()
+        self.layers, self.q, self.k_new, self.v_new = layers, q, k_new, v_new
+        self.stream = stream_ptr(q.device)
+        self.outs = [torch.empty(q.shape[0], 1, q.shape[1], D, dtype=q.dtype, device=q.device) for _ in layers]
+        self.build = build_decode_args
+        self.launches = 0
+        self.attn_events = []
+
+    def step(self, time_attention: bool):
+        lib, st = self.lib, self.stream
+        for i, layer in enumerate(self.layers):
+            before = layer._key_group_count
+            layer.update(self.k_new, self.v_new, {"materialize_full_kv": False})   # append (+ flush when due)
+            self.launches += 1 + (1 if layer._key_group_count != before else 0)
+            args = self.build(layer, self.q, D ** -0.5, None, self.outs[i])
+            if time_attention:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            rc = lib.mz_decode_attention(ctypes.byref(args), st)
+            if time_attention:
+                e1.record()
+                self.attn_events.append((e0, e1))
+            if rc != 0:
+                raise RuntimeError("mz_decode_attention failed")
+            self.launches += 2
+
+
+def run_ours(args) -> dict:
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    import muzero_b200 as mz
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    bits, L, B = args.bits, args.layers, args.batch
+    layers = build_layers(bits, device, L, B, seed=1234 + rank)
+    gen = torch.Generator(device=device).manual_seed(99 + rank)
+    q = torch.randn(B, QH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+    k_new = torch.randn(B, KVH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+    v_new = torch.randn(B, KVH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+
+    # ---------------- device-resident throughput through the C ABI
+    sess = CabiSession(layers, q, k_new, v_new)
+    for _ in range(args.warmup):
+        sess.step(False)
+    barrier()
+    sess.launches = 0
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        sess.step(True)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    attn_us = statistics.fmean(a.elapsed_time(b) for a, b in sess.attn_events) * 1e3
+    launches = sess.launches
+    ctx_now = layers[0].get_seq_length()
+
+    # ---------------- end to end through the plug-in API with host buffers
+    mz.patch_transformers()
+    from types import SimpleNamespace
+    cache = mz.MuZeroCache(layers[0].cfg)
+    cache.layers = layers
+    module = SimpleNamespace(num_key_value_groups=QH // KVH)
+    host_q = [torch.randn(B, QH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    host_k = [torch.randn(B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    host_v = [torch.randn(B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    host_out = torch.empty(L, B, 1, QH, D, dtype=torch.bfloat16).pin_memory()
+    h2d = L * (host_q[0].numel() + 2 * host_k[0].numel()) * 2
+    d2h = host_out.numel() * 2
+
+    def e2e_step(i: int):
+        outs = []
+        for li in range(L):
+            dq = host_q[i & 1].to(device, non_blocking=True)
+            dk = host_k[i & 1].to(device, non_blocking=True)
+            dv = host_v[i & 1].to(device, non_blocking=True)
+            cache.update(dk, dv, li, {"materialize_full_kv": False})
+            out, _ = mz.mu_zero_decode_attention_forward(module, dq, None, D ** -0.5, cache.get_attention_state(li))
+            host_out[li].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the step's result is on the host
+
+    for i in range(min(args.warmup, 3)):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    barrier()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+
+    peak, peak_kind = measured_peak_gbs()
+    abytes = algorithmic_bytes(bits, batch=B)
+    achieved = abytes / (attn_us * 1e-6) / 1e9
+    result = {
+        "metric": "decode tokens/sec of the KV-cache hot path (append + flush + quantized decode attention, 36 layers, batch 64/GPU, ctx 4096+128)",
+        "value": world * B * args.steps / (ms_total * 1e-3),
+        "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": f"u{bits} codes, fp16 metadata, bf16 residual, f32 accumulation",
+        "data": "synthetic",
+        "config": {"workload": f"BASELINE config 1: standalone quantized decode attention, Qwen3-8B attention shape, {L} layers/step",
+                   "bits": bits, "group": GROUP, "batch_per_gpu": B, "global_batch": B * world, "context": ctx_now,
+                   "residual_length": RES, "kv_heads": KVH, "q_heads": QH, "head_dim": D,
+                   "parallelism": f"batch-sharded x{world}, no collective",
+                   "l2_policy": f"inputs larger than L2: {L} distinct layer caches walked per step"},
+        "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "decode_tiles_kernel + combine_tiles_kernel",
+                     "bytes_per_launch": abytes, "us_per_launch": attn_us},
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(bits, seconds=12.0)
+    if world > 1:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def cpu_baseline(bits: int, seconds: float) -> dict:
+    """The oracle (CPU restatement of the reference's torch path) on a bounded sample of the workload."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("mz_oracle", os.path.join(ROOT, "oracle", "mz_oracle.py"))
+    orc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(orc)
+    sb, sl = 2, 2    # sequences and layers of the sample
+    caches = []
+    for li in range(sl):
+        k, v, q = orc.synth_kv(sb, KVH, CTX + RES, D, QH, seed=li)
+        layer = orc.OracleCacheLayer(bits=bits, group=GROUP, residual=RES)
+        layer.append(k, v)
+        caches.append((layer, q))
+    k1 = torch.randn(sb, KVH, 1, D).to(torch.bfloat16)
+    v1 = torch.randn(sb, KVH, 1, D).to(torch.bfloat16)
+    steps, t0 = 0, time.perf_counter()
+    while True:
+        for layer, q in caches:
+            layer.append(k1, v1)
+            orc.decode_attention_oracle(q, layer, D ** -0.5, QH // KVH)
+        steps += 1
+        if time.perf_counter() - t0 > seconds or steps >= 64:
+            break
+    per_layer = (time.perf_counter() - t0) / (steps * sl)
+    return {"value": sb / (per_layer * LAYERS), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{sb} of {BATCH} sequences, {sl} of {LAYERS} layers, {steps} steps; per-layer time scaled to {LAYERS} layers",
+            "host_cpus": os.cpu_count(), "torch": torch.__version__}
+
+
+def run_reference(args) -> dict:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return {}
+    t0 = time.perf_counter()
+    base = cpu_baseline(args.bits, seconds=max(10.0, min(90.0, 2.0 * args.steps)))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return {
+        "impl": "reference",
+        "metric": "decode tokens/sec of the KV-cache hot path (append + flush + quantized decode attention, 36 layers, batch 64/GPU, ctx 4096+128)",
+        "value": base["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * BATCH / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 torch CPU ops (the reference's torch backend restated)", "data": "synthetic",
+        "config": {"workload": f"BASELINE config 1: standalone quantized decode attention, Qwen3-8B attention shape, {LAYERS} layers/step",
+                   "bits": args.bits, "group": GROUP, "batch_per_gpu": BATCH, "context": CTX + RES},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

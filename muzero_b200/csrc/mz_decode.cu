@@ -1,5 +1,8 @@
 // Decode attention entry points: argument checks, split selection, workspace carving,
 // kernel dispatch, and the deterministic log-sum-exp combine.
+#include <cstdlib>
+#include <cstring>
+
 #include "mz_decode.cuh"
 
 namespace {
@@ -44,7 +47,7 @@ int sm_count() {
 struct Plan {
   MzDecodeParams p;
   bool tiles;
-  int units;
+  size_t slots;     // partial records
   size_t ws_bytes;
 };
 
@@ -73,21 +76,27 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   p.NG = (s->head_dim + s->group - 1) / s->group;
   p.eps = 1e-8f;
   p.table_k = p.table_v = nullptr;
-  plan->tiles = mz_decode_tiles_supported(p);
-  plan->units = plan->tiles ? mz_decode_units_tiles(*s) : mz_decode_units_generic(*s);
-  int splits = a->splits;
-  if (splits == 0) {
-    // aim for about two waves of CTAs over the SMs, but at least 4 units per CTA
-    const long long pairs = (long long)s->batch * s->kv_heads;
-    const long long want = (2LL * sm_count() * (plan->tiles ? 2 : 4) + pairs - 1) / pairs;
-    splits = (int)want;
-    if (splits > plan->units / 4) splits = plan->units / 4;
-    if (splits < 1) splits = 1;
+  // MZ_DECODE_KERNEL=generic routes every call to the shape-generic kernel (debugging aid)
+  const char* force = std::getenv("MZ_DECODE_KERNEL");
+  plan->tiles = mz_decode_tiles_supported(p) && !(force && std::strcmp(force, "generic") == 0);
+  if (plan->tiles) {
+    if ((rc = mz_plan_tiles(p, a->splits, sm_count(), &plan->slots))) return rc;
+    p.splits = 0;
+  } else {
+    const int units = mz_decode_units_generic(*s);
+    int splits = a->splits;
+    if (splits == 0) {
+      // aim for about two waves of CTAs over the SMs, but at least 4 units per CTA
+      const long long pairs = (long long)s->batch * s->kv_heads;
+      splits = (int)((2LL * sm_count() * 4 + pairs - 1) / pairs);
+      if (splits > units / 4) splits = units / 4;
+      if (splits < 1) splits = 1;
+    }
+    if (splits > units) splits = units;
+    p.splits = splits;
+    plan->slots = (size_t)s->batch * a->q_heads * splits;
   }
-  if (splits > plan->units) splits = plan->units;
-  p.splits = splits;
-  const size_t slots = (size_t)s->batch * a->q_heads * splits;
-  plan->ws_bytes = slots * sizeof(float) * (2 + (size_t)s->head_dim);
+  plan->ws_bytes = plan->slots * sizeof(float) * (2 + (size_t)s->head_dim);
   if (need_tables && !plan->tiles) {
     if ((rc = mz_get_expand_table(s->bits, s->alpha_key, &p.table_k))) return rc;
     if ((rc = mz_get_expand_table(s->bits, s->alpha_value, &p.table_v))) return rc;
@@ -102,11 +111,21 @@ int run_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
     return mz_fail(MZ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", plan->ws_bytes, a->workspace_bytes);
   MZ_REQUIRE((uintptr_t)a->workspace % 16 == 0, "workspace must be 16-byte aligned");
   MzDecodeParams& p = plan->p;
-  const size_t slots = (size_t)p.s.batch * p.H * p.splits;
   p.part.m = (float*)a->workspace;
-  p.part.l = p.part.m + slots;
-  p.part.acc = p.part.l + slots;
+  p.part.l = p.part.m + plan->slots;
+  p.part.acc = p.part.l + plan->slots;
   return plan->tiles ? mz_launch_decode_tiles(p, st) : mz_launch_decode_generic(p, st);
+}
+
+int finish(const Plan& plan, const MzDecodeOut& o, cudaStream_t st) {
+  const MzDecodeParams& p = plan.p;
+  if (plan.tiles) return mz_combine_tiles(p, o, st);
+  const int D = p.s.head_dim;
+  const int threads = D >= 128 ? 128 : ((D + 31) / 32) * 32;
+  lse_combine_kernel<<<(unsigned)(p.s.batch * p.H), threads, 0, st>>>(p.part.m, p.part.l, p.part.acc, p.splits, p.splits, 1, D, o.out,
+                                                                      o.out_dt, o.m, o.l, o.acc);
+  MZ_LAUNCH_CHECK("lse_combine");
+  return MZ_OK;
 }
 }  // namespace
 
@@ -119,16 +138,11 @@ extern "C" size_t mz_decode_workspace_bytes(const mz_decode_args* args) {
 extern "C" int mz_decode_attention(const mz_decode_args* a, void* stream) {
   Plan plan;
   cudaStream_t st = (cudaStream_t)stream;
+  MZ_REQUIRE(a != nullptr && a->out != nullptr && mz_dtype_ok(a->out_dtype), "bad output");
   int rc = run_partials(a, &plan, st);
   if (rc) return rc;
-  MZ_REQUIRE(a->out != nullptr && mz_dtype_ok(a->out_dtype), "bad output");
-  const MzDecodeParams& p = plan.p;
-  const int D = p.s.head_dim;
-  const int threads = D >= 128 ? 128 : ((D + 31) / 32) * 32;
-  lse_combine_kernel<<<(unsigned)(p.s.batch * p.H), threads, 0, st>>>(p.part.m, p.part.l, p.part.acc, p.splits, p.splits, 1, D, a->out,
-                                                                      a->out_dtype, nullptr, nullptr, nullptr);
-  MZ_LAUNCH_CHECK("lse_combine");
-  return MZ_OK;
+  const MzDecodeOut o = {a->out, a->out_dtype, nullptr, nullptr, nullptr};
+  return finish(plan, o, st);
 }
 
 extern "C" int mz_decode_attention_partial(const mz_decode_args* a, float* m, float* l, float* acc, void* stream) {
@@ -137,13 +151,8 @@ extern "C" int mz_decode_attention_partial(const mz_decode_args* a, float* m, fl
   MZ_REQUIRE(m && l && acc, "NULL partial output");
   int rc = run_partials(a, &plan, st);
   if (rc) return rc;
-  const MzDecodeParams& p = plan.p;
-  const int D = p.s.head_dim;
-  const int threads = D >= 128 ? 128 : ((D + 31) / 32) * 32;
-  lse_combine_kernel<<<(unsigned)(p.s.batch * p.H), threads, 0, st>>>(p.part.m, p.part.l, p.part.acc, p.splits, p.splits, 1, D, nullptr,
-                                                                      MZ_F32, m, l, acc);
-  MZ_LAUNCH_CHECK("lse_combine_partial");
-  return MZ_OK;
+  const MzDecodeOut o = {nullptr, MZ_F32, m, l, acc};
+  return finish(plan, o, st);
 }
 
 extern "C" int mz_lse_merge(const float* m, const float* l, const float* acc, int n_parts, long long rows, int head_dim, void* out,

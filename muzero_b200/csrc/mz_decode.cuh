@@ -2,11 +2,24 @@
 #pragma once
 #include "mz_store.cuh"
 
-// Partial results of one sequence split: slot = (b*H + h) * splits + split.
+// Partial results (un-normalised softmax state) written by the main kernels:
+//   m   running maximum of the scaled logits      l   sum of exp(logit - m)
+//   acc sum of exp(logit - m) * V
+// generic kernel : slot = (b*H + h) * splits + split
+// tiled kernel   : slot = (warp * max_segs + seg) * gqa + head_in_group
 struct MzPartials {
-  float* m;    // [B*H*splits]       running maximum of the scaled logits
-  float* l;    // [B*H*splits]       sum of exp(logit - m)
-  float* acc;  // [B*H*splits*D]     sum of exp(logit - m) * V
+  float* m;
+  float* l;
+  float* acc;  // [slots][D]
+};
+
+// Work decomposition of the tiled kernel: the flat list of (pair, tile) items, pair = b*KVH+kvh,
+// is cut into `total_warps` contiguous ranges, one per warp.
+struct MzTilesPlan {
+  int total_warps, warps_per_cta, ctas, max_segs;
+  int tiles_per_pair;      // k_groups + ceil(res_len / G)
+  long long total_tiles;   // pairs * tiles_per_pair
+  unsigned smem_bytes, smem_per_warp;
 };
 
 struct MzDecodeParams {
@@ -20,14 +33,21 @@ struct MzDecodeParams {
   const float* table_k;  // exact expand tables (generic kernel)
   const float* table_v;
   float eps;
+  MzTilesPlan tp;
+};
+
+// where a call's result goes: normalised output, or the merged (m, l, acc) triple
+struct MzDecodeOut {
+  void* out; int out_dt;
+  float* m; float* l; float* acc;
 };
 
 // generic kernel: any bits / group / head_dim<=512 / gqa<=16
 int mz_launch_decode_generic(const MzDecodeParams& p, cudaStream_t st);
-// tuned kernel: head_dim 128, group in {32,64,128}, gqa in {1,2,4,8}; returns MZ_ERR_UNSUPPORTED otherwise
-int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st);
-bool mz_decode_tiles_supported(const MzDecodeParams& p);
-
-// units of work a call is split over (sequence positions / unit size), per kernel family
 int mz_decode_units_generic(const mz_kv_store& s);
-int mz_decode_units_tiles(const mz_kv_store& s);
+
+// tiled kernel: head_dim 128, group in {32,64,128}, gqa in {1,2,4,8}, 16-byte aligned store
+bool mz_decode_tiles_supported(const MzDecodeParams& p);
+int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots);
+int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st);
+int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t st);

@@ -1,6 +1,572 @@
-// Tuned decode-attention kernel (placeholder until the tiled kernel lands).
-#include "mz_decode.cuh"
+// Tiled decode attention for head_dim 128 (sm_100a).
+//
+// Work item = one tile of G tokens of one (batch, kv head) pair: a packed key group
+// [128 rows x QB bytes] with its value rows [G tokens x 128 codes], or G dense residual tokens.
+// The flat list of items is cut into equal contiguous ranges, one per WARP; a warp streams its
+// range on its own: cp.async stages the next packed tile into its private shared-memory
+// buffers while it works on the current one, codes are expanded in registers through
+// per-row codebooks (<= 4 bits) or arithmetically (wider codes), all query heads of the kv
+// head are served from one read of the tile, softmax is kept online per warp in base 2, and
+// each (warp, pair) segment ends in one partial (m, l, acc) record.  A second small kernel
+// merges the records of a pair deterministically.  No atomics, no inter-CTA waits.
+#include "mz_tiles_common.cuh"
 
-bool mz_decode_tiles_supported(const MzDecodeParams&) { return false; }
-int mz_decode_units_tiles(const mz_kv_store& s) { return s.k_groups + (s.res_len + s.group - 1) / s.group; }
-int mz_launch_decode_tiles(const MzDecodeParams&, cudaStream_t) { return mz_fail(MZ_ERR_UNSUPPORTED, "tiled kernel not built"); }
+namespace mzt {
+
+template <int BITS, int G, int GQA>
+struct Warp {
+  using C = Cfg<BITS, G, GQA>;
+  uint8_t* kbuf; uint8_t* vbuf;
+  float* books; float2* pdup; float2* qdup; float* corr;
+  const float2* univ_k; const float2* univ_v;
+  int lane, o, dl;        // key phase: o = octet of tokens, dl = row within a step
+  int vt, vj;             // value phase: token parity within a step, octet of channels
+};
+
+// ---- per-row expansion data for one staged tile side (keys: 128 channel rows; values: G*NG rows)
+template <int BITS, int G, int GQA>
+__device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const uint8_t* meta, int meta_dt, const float2* univ,
+                                           float alpha, float lg2a) {
+  using C = Cfg<BITS, G, GQA>;
+  constexpr int TOP = C::NE - 1;
+  const uint8_t* lo_p = meta;
+  const uint8_t* sp_p = meta + C::META_BYTES / 2;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) {
+    const int r = w.lane + 32 * i;
+    const float lo = meta_at(lo_p, r, meta_dt);
+    const float span = meta_at(sp_p, r, meta_dt);
+    float anchor = __fdividef(-lo, fmaxf(span, 1e-8f));
+    anchor = fminf(fmaxf(anchor, 0.0f), 1.0f);
+    const int zc = __float2int_rn(anchor * (float)TOP);
+    const float A = fmaf(span, anchor, lo);
+    const float Bup = span * fmaxf(1.0f - anchor, 1e-8f);
+    const float Bdn = span * fmaxf(anchor, 1e-8f);
+    float* dst = w.books + r * C::BOOK_STRIDE;
+    if (C::BOOKS) {
+      const float2* u = univ + zc * (C::NE + 1);
+      if (C::NE >= 4) {
+#pragma unroll
+        for (int e = 0; e < C::NE; e += 4) {
+          float4 o4;
+          o4.x = fmaf(Bdn, u[e].y, fmaf(Bup, u[e].x, A));
+          o4.y = fmaf(Bdn, u[e + 1].y, fmaf(Bup, u[e + 1].x, A));
+          o4.z = fmaf(Bdn, u[e + 2].y, fmaf(Bup, u[e + 2].x, A));
+          o4.w = fmaf(Bdn, u[e + 3].y, fmaf(Bup, u[e + 3].x, A));
+          *(float4*)(dst + e) = o4;
+        }
+      } else {
+        dst[0] = fmaf(Bdn, u[0].y, fmaf(Bup, u[0].x, A));
+        dst[1] = fmaf(Bdn, u[1].y, fmaf(Bup, u[1].x, A));
+      }
+    } else {
+      const float inv_a = 1.0f / alpha;
+      const int up = max(TOP - zc, 1), dn = max(zc, 1);
+      *(float4*)dst = make_float4(A, Bup * inv_a, Bdn * inv_a, lg2a / (float)up);
+      *(float4*)(dst + 4) = make_float4(lg2a / (float)dn, __int_as_float(zc), 0.f, 0.f);
+    }
+  }
+}
+
+// ---- online softmax over one tile.  s[r][k]: base-2 logits of this lane's 8 tokens for the
+// head it owns in round r (head = r*RPS + dl).  Writes p pairs to pdup and corrections to corr.
+template <int BITS, int G, int GQA>
+__device__ __forceinline__ void softmax_tile(const Warp<BITS, G, GQA>& w, float (&s)[Cfg<BITS, G, GQA>::ROUNDS][8],
+                                             float (&m_st)[Cfg<BITS, G, GQA>::ROUNDS], float (&l_st)[Cfg<BITS, G, GQA>::ROUNDS]) {
+  using C = Cfg<BITS, G, GQA>;
+#pragma unroll
+  for (int r = 0; r < C::ROUNDS; ++r) {
+    const int h = r * C::RPS + w.dl;
+    float mx = s[r][0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) mx = fmaxf(mx, s[r][k]);
+#pragma unroll
+    for (int off = 1; off < C::LPR; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    const float m_new = fmaxf(m_st[r], mx);
+    const bool dead = !(m_new > -INFINITY);
+    float sum = 0.f;
+    float pr[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      pr[k] = dead ? 0.f : ex2f(s[r][k] - m_new);
+      sum += pr[k];
+    }
+#pragma unroll
+    for (int off = 1; off < C::LPR; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float c = dead ? 1.0f : ex2f(m_st[r] - m_new);   // m_st = -inf -> 0
+    l_st[r] = l_st[r] * c + sum;
+    m_st[r] = m_new;
+    if (h < GQA) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w.pdup[(w.o * 8 + k) * GQA + h] = make_float2(pr[k], pr[k]);
+      if (w.o == 0) w.corr[h] = c;
+    }
+  }
+}
+
+template <int BITS, int G, int GQA>
+__global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodeParams p) {
+  using C = Cfg<BITS, G, GQA>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const mz_kv_store& s = p.s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // universal signed shape tables: row zc, entry e -> (up part, down part) of the normalised value
+  float2* univ_k = (float2*)smem;
+  float2* univ_v = univ_k + C::UNIV_FLOAT2;
+  if (C::BOOKS) {
+    constexpr int TOP = C::NE - 1;
+    for (int i = threadIdx.x; i < 2 * C::NE * C::NE; i += blockDim.x) {
+      const int which = i / (C::NE * C::NE), j = i % (C::NE * C::NE);
+      const int zc = j / C::NE, e = j % C::NE;
+      const float alpha = which ? s.alpha_value : s.alpha_key;
+      const float lb = log1pf(alpha);
+      float2 u = make_float2(0.f, 0.f);
+      if (e >= zc) {
+        const int up = max(TOP - zc, 1);
+        u.x = expm1f((float)min(e - zc, up) / (float)up * lb) / alpha;
+      } else {
+        const int dn = max(zc, 1);
+        u.y = -expm1f((float)(zc - e) / (float)dn * lb) / alpha;
+      }
+      (which ? univ_v : univ_k)[zc * (C::NE + 1) + e] = u;
+    }
+  }
+  __syncthreads();
+
+  const long long N = p.tp.total_tiles;
+  const int W = p.tp.total_warps, T = p.tp.tiles_per_pair;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (gw >= W) return;
+  const long long f0 = (long long)gw * N / W, f1 = (long long)(gw + 1) * N / W;
+  if (f0 >= f1) return;
+
+  Warp<BITS, G, GQA> w;
+  uint8_t* base = smem + C::SHARED + (size_t)warp * C::PER_WARP;
+  w.kbuf = base;
+  w.vbuf = w.kbuf + C::KBUF;
+  w.books = (float*)(w.vbuf + C::VBUF);
+  w.pdup = (float2*)((uint8_t*)w.books + C::BOOK_BYTES);
+  w.qdup = (float2*)((uint8_t*)w.pdup + C::PDUP);
+  w.corr = (float*)((uint8_t*)w.qdup + C::QDUP);
+  w.univ_k = univ_k; w.univ_v = univ_v;
+  w.lane = lane; w.o = lane % C::LPR; w.dl = lane / C::LPR;
+  w.vt = lane >> 4; w.vj = lane & 15;
+
+  const int msz = s.meta_dtype == MZ_F32 ? 4 : 2;
+  const float lg2a_k = log2f(1.0f + s.alpha_key), lg2a_v = log2f(1.0f + s.alpha_value);
+  const int nq = s.k_groups * G;
+
+  auto stage_k = [&](long long f) {
+    if (f < f1) {
+      const int pair = (int)(f / T), tile = (int)(f % T);
+      if (tile < s.k_groups) {
+        const int b = pair / s.kv_heads, kvh = pair % s.kv_heads;
+        const uint8_t* src = s.packed_k + b * s.pk_stride_b + kvh * s.pk_stride_h + (long long)tile * C::TILE_BYTES;
+        warp_copy_async(w.kbuf, src, C::TILE_BYTES, lane);
+        const long long m0 = (b * s.km_stride_b + kvh * s.km_stride_h + (long long)tile * D) * msz;
+        warp_copy_async(w.kbuf + C::TILE_BYTES, (const uint8_t*)s.k_mn + m0, D * msz, lane);
+        warp_copy_async(w.kbuf + C::TILE_BYTES + C::META_BYTES / 2, (const uint8_t*)s.k_scale + m0, D * msz, lane);
+      }
+    }
+    cp_async_commit();
+  };
+  auto stage_v = [&](long long f) {
+    if (f < f1) {
+      const int pair = (int)(f / T), tile = (int)(f % T);
+      if (tile < s.k_groups) {
+        const int b = pair / s.kv_heads, kvh = pair % s.kv_heads;
+        const uint8_t* src = s.packed_v + b * s.pv_stride_b + kvh * s.pv_stride_h + (long long)tile * C::TILE_BYTES;
+        warp_copy_async(w.vbuf, src, C::TILE_BYTES, lane);
+        const long long m0 = (b * s.vm_stride_b + kvh * s.vm_stride_h + (long long)tile * D) * msz;
+        warp_copy_async(w.vbuf + C::TILE_BYTES, (const uint8_t*)s.v_mn + m0, D * msz, lane);
+        warp_copy_async(w.vbuf + C::TILE_BYTES + C::META_BYTES / 2, (const uint8_t*)s.v_scale + m0, D * msz, lane);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float2 out2[4][GQA];
+  float m_st[C::ROUNDS], l_st[C::ROUNDS];
+  int cur_pair = -1, seg = 0;
+
+  auto reset_state = [&]() {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) out2[j][h] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < C::ROUNDS; ++r) { m_st[r] = -INFINITY; l_st[r] = 0.f; }
+  };
+  auto write_partial = [&]() {
+    const long long slot0 = ((long long)gw * p.tp.max_segs + seg) * GQA;
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+      float2 t[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        t[j].x = out2[j][h].x + __shfl_xor_sync(0xffffffffu, out2[j][h].x, 16);
+        t[j].y = out2[j][h].y + __shfl_xor_sync(0xffffffffu, out2[j][h].y, 16);
+      }
+      if (lane < 16) {
+        float4* dst = (float4*)(p.part.acc + (slot0 + h) * D + lane * 8);
+        dst[0] = make_float4(t[0].x, t[0].y, t[1].x, t[1].y);
+        dst[1] = make_float4(t[2].x, t[2].y, t[3].x, t[3].y);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < C::ROUNDS; ++r) {
+      const int h = r * C::RPS + w.dl;
+      if (h < GQA && w.o == 0) {
+        p.part.m[slot0 + h] = m_st[r] * (1.0f / LOG2E);   // back to natural-log units
+        p.part.l[slot0 + h] = l_st[r];
+      }
+    }
+  };
+
+  stage_k(f0);
+  stage_v(f0);
+  for (long long f = f0; f < f1; ++f) {
+    const int pair = (int)(f / T), tile = (int)(f % T);
+    const int b = pair / s.kv_heads, kvh = pair % s.kv_heads;
+    if (pair != cur_pair) {
+      if (cur_pair >= 0) { write_partial(); ++seg; }
+      cur_pair = pair;
+      reset_state();
+      __syncwarp();
+      const float qs = p.scaling * LOG2E;
+      for (int i = lane; i < D * GQA; i += 32) {
+        const int d = i / GQA, h = i % GQA;
+        const float q = mz_load_as_float(p.query, b * p.q_stride_b + (long long)(kvh * GQA + h) * p.q_stride_h + d, s.kv_dtype) * qs;
+        w.qdup[i] = make_float2(q, q);
+      }
+      __syncwarp();
+    }
+    const bool dense = tile >= s.k_groups;
+    const int tok0 = dense ? (tile - s.k_groups) * G : tile * G;      // first token inside its region
+    const int ntok = dense ? min(G, s.res_len - tok0) : G;
+    const long long mask0 = p.mask ? b * p.mask_stride_b + (dense ? nq : 0) + tok0 : 0;
+    float sl[C::ROUNDS][8];
+
+    cp_async_wait<1>();
+    __syncwarp();
+    if (!dense) {
+      // ---------------- keys: expansion data, then QK with all heads per code
+      build_rows<BITS, G, GQA>(w, w.kbuf + C::TILE_BYTES, s.meta_dtype, w.univ_k, s.alpha_key, lg2a_k);
+      __syncwarp();
+      float2 acc[4][GQA];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) acc[j][h] = make_float2(0.f, 0.f);
+#pragma unroll 2
+      for (int step = 0; step < D / C::RPS; ++step) {
+        const int d = step * C::RPS + w.dl;
+        const unsigned long long codes = load_octet<BITS>(w.kbuf + d * C::QB + w.o * BITS);
+        float v[8];
+        expand8<BITS, C::BOOKS>(codes, w.books + d * C::BOOK_STRIDE, v);
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+          const float2 qq = w.qdup[d * GQA + h];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ffma2(acc[j][h], make_float2(v[2 * j], v[2 * j + 1]), qq);
+        }
+      }
+      // sum over the rows handled by the other lanes of this token octet
+#pragma unroll
+      for (int off = C::LPR; off < 32; off <<= 1)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int h = 0; h < GQA; ++h) {
+            acc[j][h].x += __shfl_xor_sync(0xffffffffu, acc[j][h].x, off);
+            acc[j][h].y += __shfl_xor_sync(0xffffffffu, acc[j][h].y, off);
+          }
+#pragma unroll
+      for (int r = 0; r < C::ROUNDS; ++r)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          float val = 0.f;
+#pragma unroll
+          for (int h = 0; h < GQA; ++h)
+            if (h / C::RPS == r && h % C::RPS == w.dl) val = (k & 1) ? acc[k >> 1][h].y : acc[k >> 1][h].x;
+          sl[r][k] = val;
+        }
+    } else {
+      // ---------------- dense residual keys: one token per lane, logits exchanged through shared memory
+      float* sbuf = (float*)w.pdup;
+      const uint16_t* rk = (const uint16_t*)s.res_k + b * s.res_stride_b + kvh * s.res_stride_h;
+#pragma unroll 1
+      for (int i = 0; i < G / 32; ++i) {
+        const int t = lane + 32 * i;
+        float dot[GQA];
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) dot[h] = 0.f;
+        if (t < ntok) {
+          const uint4* row = (const uint4*)(rk + (long long)(s.res_start + tok0 + t) * s.res_stride_t);
+#pragma unroll 4
+          for (int c = 0; c < D / 8; ++c) {
+            const uint4 raw = __ldg(row + c);
+            const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x = unpack2(ww[e], s.kv_dtype);
+              const int d = c * 8 + 2 * e;
+#pragma unroll
+              for (int h = 0; h < GQA; ++h) {
+                dot[h] = fmaf(x.x, w.qdup[d * GQA + h].x, dot[h]);
+                dot[h] = fmaf(x.y, w.qdup[(d + 1) * GQA + h].x, dot[h]);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) sbuf[t * GQA + h] = t < ntok ? dot[h] : -INFINITY;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int r = 0; r < C::ROUNDS; ++r) {
+        const int h = min(r * C::RPS + w.dl, GQA - 1);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sl[r][k] = sbuf[(w.o * 8 + k) * GQA + h];
+      }
+    }
+    __syncwarp();                 // every lane is done with kbuf, books and sbuf
+    stage_k(f + 1);
+    if (p.mask) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int t = w.o * 8 + k;
+        const float mv = t < ntok ? mz_load_as_float(p.mask, mask0 + t, p.mask_dtype) * LOG2E : 0.f;
+#pragma unroll
+        for (int r = 0; r < C::ROUNDS; ++r) sl[r][k] += mv;
+      }
+    }
+    softmax_tile<BITS, G, GQA>(w, sl, m_st, l_st);
+    cp_async_wait<1>();
+    __syncwarp();                 // value tile landed; p pairs and corrections visible
+    {
+      bool rescale = false;
+      float cr[GQA];
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) { cr[h] = w.corr[h]; rescale |= cr[h] != 1.0f; }
+      if (rescale) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int h = 0; h < GQA; ++h) { out2[j][h].x *= cr[h]; out2[j][h].y *= cr[h]; }
+      }
+    }
+    if (!dense) {
+      build_rows<BITS, G, GQA>(w, w.vbuf + C::TILE_BYTES, s.meta_dtype, w.univ_v, s.alpha_value, lg2a_v);
+      __syncwarp();
+#pragma unroll 2
+      for (int step = 0; step < G / 2; ++step) {
+        const int t = 2 * step + w.vt;
+        const unsigned long long codes = load_octet<BITS>(w.vbuf + t * (16 * BITS) + w.vj * BITS);
+        float v[8];
+        expand8<BITS, C::BOOKS>(codes, w.books + (t * C::NG + (w.vj * 8) / G) * C::BOOK_STRIDE, v);
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+          const float2 pp = w.pdup[t * GQA + h];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ffma2(out2[j][h], make_float2(v[2 * j], v[2 * j + 1]), pp);
+        }
+      }
+    } else {
+      const uint16_t* rv = (const uint16_t*)s.res_v + b * s.res_stride_b + kvh * s.res_stride_h + w.vj * 8;
+#pragma unroll 2
+      for (int step = 0; step < G / 2; ++step) {
+        const int t = 2 * step + w.vt;
+        if (t < ntok) {
+          const uint4 raw = __ldg((const uint4*)(rv + (long long)(s.res_start + tok0 + t) * s.res_stride_t));
+          const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int h = 0; h < GQA; ++h) {
+            const float2 pp = w.pdup[t * GQA + h];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ffma2(out2[j][h], unpack2(ww[j], s.kv_dtype), pp);
+          }
+        }
+      }
+    }
+    __syncwarp();                 // every lane is done with vbuf, books and pdup
+    stage_v(f + 1);
+  }
+  cp_async_wait<0>();
+  write_partial();
+}
+
+// ---- merge of the records of one (batch, kv head) pair
+__global__ void __launch_bounds__(128) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
+  const int pair = blockIdx.x, d = threadIdx.x;
+  const long long N = p.tp.total_tiles;
+  const int W = p.tp.total_warps, T = p.tp.tiles_per_pair, gqa = p.gqa;
+  const long long lo = (long long)pair * T, hi = lo + T;
+  long long g = lo * W / N;
+  if (g >= W) g = W - 1;
+  while (g + 1 < W && (g + 1) * N / W <= lo) ++g;
+  while (g > 0 && g * N / W > lo) --g;
+  const int g_first = (int)g;
+  for (int h = 0; h < gqa; ++h) {
+    float mx = -INFINITY;
+    for (int gw = g_first; gw < W; ++gw) {
+      const long long f0 = (long long)gw * N / W, f1 = (long long)(gw + 1) * N / W;
+      if (f0 >= hi) break;
+      if (f1 <= lo || f0 >= f1) continue;
+      const long long slot = ((long long)gw * p.tp.max_segs + (pair - (int)(f0 / T))) * gqa + h;
+      mx = fmaxf(mx, p.part.m[slot]);
+    }
+    float lsum = 0.f, a = 0.f;
+    for (int gw = g_first; gw < W; ++gw) {
+      const long long f0 = (long long)gw * N / W, f1 = (long long)(gw + 1) * N / W;
+      if (f0 >= hi) break;
+      if (f1 <= lo || f0 >= f1) continue;
+      const long long slot = ((long long)gw * p.tp.max_segs + (pair - (int)(f0 / T))) * gqa + h;
+      const float mi = p.part.m[slot];
+      const float wgt = mi > -INFINITY ? __expf(mi - mx) : 0.f;
+      lsum = fmaf(p.part.l[slot], wgt, lsum);
+      a = fmaf(p.part.acc[slot * D + d], wgt, a);
+    }
+    const long long row = (long long)pair * gqa + h;
+    if (o.out) mz_store_from_float(o.out, row * D + d, a / fmaxf(lsum, 1e-20f), o.out_dt);
+    else {
+      o.acc[row * D + d] = a;
+      if (d == 0) { o.m[row] = mx; o.l[row] = lsum; }
+    }
+  }
+}
+
+template <int BITS, int G, int GQA>
+int launch_one(const MzDecodeParams& p, cudaStream_t st) {
+  auto kern = decode_tiles_kernel<BITS, G, GQA>;
+  if (p.tp.smem_bytes > 48 * 1024) MZ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.tp.smem_bytes));
+  kern<<<(unsigned)p.tp.ctas, p.tp.warps_per_cta * 32, p.tp.smem_bytes, st>>>(p);
+  MZ_LAUNCH_CHECK("decode_tiles");
+  return MZ_OK;
+}
+
+template <int BITS, int G>
+int launch_gqa(const MzDecodeParams& p, cudaStream_t st) {
+  switch (p.gqa) {
+    case 1: return launch_one<BITS, G, 1>(p, st);
+    case 2: return launch_one<BITS, G, 2>(p, st);
+    case 4: return launch_one<BITS, G, 4>(p, st);
+    case 8: return launch_one<BITS, G, 8>(p, st);
+  }
+  return mz_fail(MZ_ERR_UNSUPPORTED, "gqa %d", p.gqa);
+}
+
+template <int BITS>
+int launch_group(const MzDecodeParams& p, cudaStream_t st) {
+  switch (p.s.group) {
+    case 32: return launch_gqa<BITS, 32>(p, st);
+    case 64: return launch_gqa<BITS, 64>(p, st);
+    case 128: return launch_gqa<BITS, 128>(p, st);
+  }
+  return mz_fail(MZ_ERR_UNSUPPORTED, "group %d", p.s.group);
+}
+
+template <int BITS, int G, int GQA>
+void sizes_one(unsigned* per_warp, unsigned* shared) {
+  *per_warp = Cfg<BITS, G, GQA>::PER_WARP;
+  *shared = Cfg<BITS, G, GQA>::SHARED;
+}
+template <int BITS, int G>
+void sizes_gqa(int gqa, unsigned* a, unsigned* b) {
+  if (gqa == 1) sizes_one<BITS, G, 1>(a, b);
+  else if (gqa == 2) sizes_one<BITS, G, 2>(a, b);
+  else if (gqa == 4) sizes_one<BITS, G, 4>(a, b);
+  else sizes_one<BITS, G, 8>(a, b);
+}
+template <int BITS>
+void sizes_group(int group, int gqa, unsigned* a, unsigned* b) {
+  if (group == 32) sizes_gqa<BITS, 32>(gqa, a, b);
+  else if (group == 64) sizes_gqa<BITS, 64>(gqa, a, b);
+  else sizes_gqa<BITS, 128>(gqa, a, b);
+}
+void sizes_any(int bits, int group, int gqa, unsigned* a, unsigned* b) {
+  switch (bits) {
+    case 1: sizes_group<1>(group, gqa, a, b); break;
+    case 2: sizes_group<2>(group, gqa, a, b); break;
+    case 3: sizes_group<3>(group, gqa, a, b); break;
+    case 4: sizes_group<4>(group, gqa, a, b); break;
+    case 5: sizes_group<5>(group, gqa, a, b); break;
+    case 6: sizes_group<6>(group, gqa, a, b); break;
+    case 7: sizes_group<7>(group, gqa, a, b); break;
+    default: sizes_group<8>(group, gqa, a, b); break;
+  }
+}
+}  // namespace mzt
+
+bool mz_decode_tiles_supported(const MzDecodeParams& p) {
+  const mz_kv_store& s = p.s;
+  if (s.head_dim != 128) return false;
+  if (s.group != 32 && s.group != 64 && s.group != 128) return false;
+  if (p.gqa != 1 && p.gqa != 2 && p.gqa != 4 && p.gqa != 8) return false;
+  auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+  const int msz = s.meta_dtype == MZ_F32 ? 4 : 2;
+  if (s.k_groups > 0) {
+    if (!al16(s.packed_k) || !al16(s.packed_v) || !al16(s.k_mn) || !al16(s.k_scale) || !al16(s.v_mn) || !al16(s.v_scale)) return false;
+    if ((s.pk_stride_b | s.pk_stride_h | s.pv_stride_b | s.pv_stride_h) & 15) return false;
+    if (((s.km_stride_b | s.km_stride_h | s.vm_stride_b | s.vm_stride_h) * msz) & 15) return false;
+  }
+  if (s.res_len > 0) {
+    if (!al16(s.res_k) || !al16(s.res_v)) return false;
+    if ((s.res_stride_b | s.res_stride_h | s.res_stride_t) & 7) return false;
+  }
+  return true;
+}
+
+int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots) {
+  const mz_kv_store& s = p.s;
+  MzTilesPlan& t = p.tp;
+  unsigned per_warp = 0, shared = 0;
+  mzt::sizes_any(s.bits, s.group, p.gqa, &per_warp, &shared);
+  const unsigned budget = 220 * 1024;
+  int warps = (int)((budget - shared) / per_warp);
+  if (warps < 1) return mz_fail(MZ_ERR_UNSUPPORTED, "tile does not fit shared memory");
+  if (warps > 8) warps = 8;
+  t.warps_per_cta = warps;
+  t.smem_per_warp = per_warp;
+  t.smem_bytes = shared + per_warp * warps;
+  t.tiles_per_pair = s.k_groups + (s.res_len + s.group - 1) / s.group;
+  const long long pairs = (long long)s.batch * s.kv_heads;
+  t.total_tiles = pairs * t.tiles_per_pair;
+  long long W;
+  if (splits_request > 0) {
+    W = pairs * splits_request;
+  } else {
+    W = (long long)sm_count * warps;              // one resident CTA per SM
+    if (W > t.total_tiles / 2) W = t.total_tiles / 2;   // at least two tiles per warp
+    if (W < 1) W = 1;
+  }
+  if (W > (1LL << 30)) return mz_fail(MZ_ERR_ARG, "too many splits");
+  t.total_warps = (int)W;
+  t.ctas = (int)((W + warps - 1) / warps);
+  const long long len = (t.total_tiles + W - 1) / W;
+  t.max_segs = (int)((len + t.tiles_per_pair - 2) / t.tiles_per_pair + 1);
+  if (t.max_segs < 1) t.max_segs = 1;
+  *slots = (size_t)W * t.max_segs * p.gqa;
+  return MZ_OK;
+}
+
+int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st) {
+  switch (p.s.bits) {
+    case 1: return mzt::launch_group<1>(p, st);
+    case 2: return mzt::launch_group<2>(p, st);
+    case 3: return mzt::launch_group<3>(p, st);
+    case 4: return mzt::launch_group<4>(p, st);
+    case 5: return mzt::launch_group<5>(p, st);
+    case 6: return mzt::launch_group<6>(p, st);
+    case 7: return mzt::launch_group<7>(p, st);
+    case 8: return mzt::launch_group<8>(p, st);
+  }
+  return mz_fail(MZ_ERR_UNSUPPORTED, "bits %d", p.s.bits);
+}
+
+int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t st) {
+  mzt::combine_tiles_kernel<<<(unsigned)(p.s.batch * p.s.kv_heads), 128, 0, st>>>(p, o);
+  MZ_LAUNCH_CHECK("combine_tiles");
+  return MZ_OK;
+}

@@ -51,15 +51,20 @@ struct MzQuantRow {
   }
 
   __device__ __forceinline__ int code(float x) const {
+    // NaN (0/0 when the row range or a side extent rounds to zero in T) propagates through the
+    // reference's chain and its final cast to uint8 yields 0; mirror that outcome.
     float unit = TT::round(__fdiv_rn(TT::round(__fsub_rn(x, lo)), span));
+    if (unit != unit || anchor != anchor) return 0;
     unit = fminf(fmaxf(unit, 0.0f), 1.0f);
     float q;
     if (unit >= anchor) {
       float p = TT::round(__fdiv_rn(TT::round(__fsub_rn(unit, anchor)), room_up));
+      if (p != p) return 0;
       p = fminf(fmaxf(p, 0.0f), 1.0f);
       q = TT::round(__fadd_rn(zero_code, rintf(TT::round(__fmul_rn(compand(p), steps_up)))));
     } else {
       float p = TT::round(__fdiv_rn(TT::round(__fsub_rn(anchor, unit)), room_dn));
+      if (p != p) return 0;
       p = fminf(fmaxf(p, 0.0f), 1.0f);
       q = TT::round(__fsub_rn(zero_code, rintf(TT::round(__fmul_rn(compand(p), steps_dn)))));
     }
