@@ -11,6 +11,13 @@
 // merges the records of a pair deterministically.  No atomics, no inter-CTA waits.
 #include "mz_tiles_common.cuh"
 
+#ifdef MZ_DEBUG_DUMP
+__device__ float g_mz_dbg[1 << 16];
+extern "C" int mz_debug_read(float* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_mz_dbg, sizeof(float) * n);
+}
+#endif
+
 namespace mzt {
 
 template <int BITS, int G, int GQA>
@@ -36,9 +43,11 @@ __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const ui
     const int r = w.lane + 32 * i;
     const float lo = meta_at(lo_p, r, meta_dt);
     const float span = meta_at(sp_p, r, meta_dt);
-    float anchor = __fdividef(-lo, fmaxf(span, 1e-8f));
+    // IEEE division and multiply: the zero code must round exactly as the dequantizer's does
+    // (a symmetric row has anchor == 0.5 and anchor*TOP on a rounding tie)
+    float anchor = __fdiv_rn(__fsub_rn(0.0f, lo), fmaxf(span, 1e-8f));
     anchor = fminf(fmaxf(anchor, 0.0f), 1.0f);
-    const int zc = __float2int_rn(anchor * (float)TOP);
+    const int zc = __float2int_rn(__fmul_rn(anchor, (float)TOP));
     const float A = fmaf(span, anchor, lo);
     const float Bup = span * fmaxf(1.0f - anchor, 1e-8f);
     const float Bdn = span * fmaxf(anchor, 1e-8f);
@@ -272,6 +281,13 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
           for (int j = 0; j < 4; ++j) ffma2(acc[j][h], make_float2(v[2 * j], v[2 * j + 1]), qq);
         }
       }
+#ifdef MZ_DEBUG_DUMP
+      if (gw == 0 && f == f0) {
+        for (int i = lane; i < D * C::NE; i += 32) g_mz_dbg[4096 + i] = w.books[(i / C::NE) * C::BOOK_STRIDE + (i % C::NE)];
+        for (int i = lane; i < D; i += 32) { g_mz_dbg[8192 + i] = meta_at(w.kbuf + C::TILE_BYTES, i, s.meta_dtype); g_mz_dbg[8192 + 128 + i] = meta_at(w.kbuf + C::TILE_BYTES + C::META_BYTES / 2, i, s.meta_dtype); }
+        for (int i = lane; i < C::TILE_BYTES / 4; i += 32) g_mz_dbg[16384 + i] = __uint_as_float(((const uint32_t*)w.kbuf)[i]);
+      }
+#endif
       // sum over the rows handled by the other lanes of this token octet
 #pragma unroll
       for (int off = C::LPR; off < 32; off <<= 1)
@@ -331,6 +347,16 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
         for (int k = 0; k < 8; ++k) sl[r][k] = sbuf[(w.o * 8 + k) * GQA + h];
       }
     }
+#ifdef MZ_DEBUG_DUMP
+    if (gw == 0 && f == f0) {
+#pragma unroll
+      for (int r = 0; r < C::ROUNDS; ++r) {
+        const int h = r * C::RPS + w.dl;
+        if (h < GQA)
+          for (int k = 0; k < 8; ++k) g_mz_dbg[h * G + w.o * 8 + k] = sl[r][k];
+      }
+    }
+#endif
     __syncwarp();                 // every lane is done with kbuf, books and sbuf
     stage_k(f + 1);
     if (p.mask) {

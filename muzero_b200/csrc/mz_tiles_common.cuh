@@ -16,7 +16,7 @@ struct Cfg {
   static constexpr int NG = D / G;                 // value groups per token
   static constexpr int TILE_BYTES = D * QB;        // packed bytes of a key tile == of a value tile
   static constexpr bool BOOKS = BITS <= 4;         // per-row codebooks; wider codes are expanded arithmetically
-  static constexpr int BOOK_STRIDE = !BOOKS ? 8 : (NE == 16 ? 20 : (NE == 8 ? 12 : NE));  // floats per row (padded vs bank conflicts)
+  static constexpr int BOOK_STRIDE = !BOOKS ? 8 : NE;   // floats per row
   static constexpr int ROUNDS = (GQA + RPS - 1) / RPS;  // softmax rounds: a lane owns head r*RPS+dl in round r
   static constexpr int META_BYTES = 1024;          // 2 x 128 entries x up to 4 bytes
   // per-warp shared memory, in bytes (every region 16-byte aligned)
@@ -100,7 +100,7 @@ __device__ __forceinline__ void expand8(unsigned long long codes, const float* _
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const int sh = BITS * k - 2;
-      const uint32_t off = sh >= 0 ? ((c32 >> sh) & (MASK << 2)) : ((c32 << 2) & (MASK << 2));
+      const uint32_t off = sh >= 0 ? ((c32 >> (sh >= 0 ? sh : 0)) & (MASK << 2)) : ((c32 << (sh < 0 ? -sh : 0)) & (MASK << 2));
       v[k] = *(const float*)((const uint8_t*)row + off);
     }
   } else {

@@ -12,7 +12,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_longlong, c_s
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libmuzero_b200.so")
+LIB_PATH = os.environ.get("MUZERO_B200_LIB") or os.path.join(os.path.dirname(_HERE), "lib", "libmuzero_b200.so")
 
 MZ_F32, MZ_F16, MZ_BF16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: MZ_F32, torch.float16: MZ_F16, torch.bfloat16: MZ_BF16}
