@@ -9,14 +9,10 @@
 // head are served from one read of the tile, softmax is kept online per warp in base 2, and
 // each (warp, pair) segment ends in one partial (m, l, acc) record.  A second small kernel
 // merges the records of a pair deterministically.  No atomics, no inter-CTA waits.
-#include "mz_tiles_common.cuh"
+#include <cstdlib>
+#include <type_traits>
 
-#ifdef MZ_DEBUG_DUMP
-__device__ float g_mz_dbg[1 << 16];
-extern "C" int mz_debug_read(float* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_mz_dbg, sizeof(float) * n);
-}
-#endif
+#include "mz_tiles_common.cuh"
 
 namespace mzt {
 
@@ -51,7 +47,7 @@ __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const ui
     const float A = fmaf(span, anchor, lo);
     const float Bup = span * fmaxf(1.0f - anchor, 1e-8f);
     const float Bdn = span * fmaxf(anchor, 1e-8f);
-    float* dst = w.books + r * C::BOOK_STRIDE;
+    float* dst = w.books + ((r % C::RPS) * C::STEPS + r / C::RPS) * C::BOOK_STRIDE;
     if (C::BOOKS) {
       const float2* u = univ + zc * (C::NE + 1);
       if (C::NE >= 4) {
@@ -121,7 +117,8 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // universal signed shape tables: row zc, entry e -> (up part, down part) of the normalised value
-  float2* univ_k = (float2*)smem;
+  uint8_t* smem_al = smem + ((256u - ((unsigned)__cvta_generic_to_shared(smem) & 255u)) & 255u);
+  float2* univ_k = (float2*)smem_al;
   float2* univ_v = univ_k + C::UNIV_FLOAT2;
   if (C::BOOKS) {
     constexpr int TOP = C::NE - 1;
@@ -151,11 +148,11 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
   if (f0 >= f1) return;
 
   Warp<BITS, G, GQA> w;
-  uint8_t* base = smem + C::SHARED + (size_t)warp * C::PER_WARP;
-  w.kbuf = base;
+  uint8_t* base = smem_al + (C::SHARED - 256) + (size_t)warp * C::PER_WARP;   // 256-byte aligned
+  w.books = (float*)base;
+  w.kbuf = base + C::BOOK_BYTES;
   w.vbuf = w.kbuf + C::KBUF;
-  w.books = (float*)(w.vbuf + C::VBUF);
-  w.pdup = (float2*)((uint8_t*)w.books + C::BOOK_BYTES);
+  w.pdup = (float2*)(w.vbuf + C::VBUF);
   w.qdup = (float2*)((uint8_t*)w.pdup + C::PDUP);
   w.corr = (float*)((uint8_t*)w.qdup + C::QDUP);
   w.univ_k = univ_k; w.univ_v = univ_v;
@@ -268,26 +265,32 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int h = 0; h < GQA; ++h) acc[j][h] = make_float2(0.f, 0.f);
-#pragma unroll 2
-      for (int step = 0; step < D / C::RPS; ++step) {
-        const int d = step * C::RPS + w.dl;
-        const unsigned long long codes = load_octet<BITS>(w.kbuf + d * C::QB + w.o * BITS);
-        float v[8];
-        expand8<BITS, C::BOOKS>(codes, w.books + d * C::BOOK_STRIDE, v);
+      {
+        const uint32_t rb_lane = (uint32_t)__cvta_generic_to_shared(w.books) + w.dl * C::LANE_BLOCK_BYTES;
+        const uint8_t* kc = w.kbuf + w.dl * C::QB + w.o * BITS;
+        const float2* qd = w.qdup + w.dl * GQA;
+#pragma unroll 1
+        for (int sb = 0; sb < C::STEPS; sb += C::UNROLL) {
+          const uint32_t rb = rb_lane + sb * C::ROW_BYTES;
+          auto one_step = [&](auto uc) {
+            constexpr int u = decltype(uc)::value;
+            const int step = sb + u;
+            const unsigned long long codes = load_octet<BITS>(kc + step * (C::RPS * C::QB));
+            float v[8];
+            expand8<BITS, C::BOOKS, C::PRMT_ADDR, u * C::ROW_BYTES>(codes, rb, v);
 #pragma unroll
-        for (int h = 0; h < GQA; ++h) {
-          const float2 qq = w.qdup[d * GQA + h];
+            for (int h = 0; h < GQA; ++h) {
+              const float2 qq = qd[step * (C::RPS * GQA) + h];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) ffma2(acc[j][h], make_float2(v[2 * j], v[2 * j + 1]), qq);
+              for (int j = 0; j < 4; ++j) ffma2(acc[j][h], make_float2(v[2 * j], v[2 * j + 1]), qq);
+            }
+          };
+          one_step(std::integral_constant<int, 0>{});
+          one_step(std::integral_constant<int, 1>{});
+          one_step(std::integral_constant<int, 2>{});
+          one_step(std::integral_constant<int, 3>{});
         }
       }
-#ifdef MZ_DEBUG_DUMP
-      if (gw == 0 && f == f0) {
-        for (int i = lane; i < D * C::NE; i += 32) g_mz_dbg[4096 + i] = w.books[(i / C::NE) * C::BOOK_STRIDE + (i % C::NE)];
-        for (int i = lane; i < D; i += 32) { g_mz_dbg[8192 + i] = meta_at(w.kbuf + C::TILE_BYTES, i, s.meta_dtype); g_mz_dbg[8192 + 128 + i] = meta_at(w.kbuf + C::TILE_BYTES + C::META_BYTES / 2, i, s.meta_dtype); }
-        for (int i = lane; i < C::TILE_BYTES / 4; i += 32) g_mz_dbg[16384 + i] = __uint_as_float(((const uint32_t*)w.kbuf)[i]);
-      }
-#endif
       // sum over the rows handled by the other lanes of this token octet
 #pragma unroll
       for (int off = C::LPR; off < 32; off <<= 1)
@@ -347,16 +350,6 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
         for (int k = 0; k < 8; ++k) sl[r][k] = sbuf[(w.o * 8 + k) * GQA + h];
       }
     }
-#ifdef MZ_DEBUG_DUMP
-    if (gw == 0 && f == f0) {
-#pragma unroll
-      for (int r = 0; r < C::ROUNDS; ++r) {
-        const int h = r * C::RPS + w.dl;
-        if (h < GQA)
-          for (int k = 0; k < 8; ++k) g_mz_dbg[h * G + w.o * 8 + k] = sl[r][k];
-      }
-    }
-#endif
     __syncwarp();                 // every lane is done with kbuf, books and sbuf
     stage_k(f + 1);
     if (p.mask) {
@@ -386,17 +379,31 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
     if (!dense) {
       build_rows<BITS, G, GQA>(w, w.vbuf + C::TILE_BYTES, s.meta_dtype, w.univ_v, s.alpha_value, lg2a_v);
       __syncwarp();
-#pragma unroll 2
-      for (int step = 0; step < G / 2; ++step) {
-        const int t = 2 * step + w.vt;
-        const unsigned long long codes = load_octet<BITS>(w.vbuf + t * (16 * BITS) + w.vj * BITS);
-        float v[8];
-        expand8<BITS, C::BOOKS>(codes, w.books + (t * C::NG + (w.vj * 8) / G) * C::BOOK_STRIDE, v);
+      {
+        const int lane_row = w.vt * C::NG + (w.vj * 8) / G;
+        const uint32_t rb_lane = (uint32_t)__cvta_generic_to_shared(w.books) + lane_row * C::LANE_BLOCK_BYTES;
+        const uint8_t* vc = w.vbuf + w.vt * (16 * BITS) + w.vj * BITS;
+        const float2* pd = w.pdup + w.vt * GQA;
+#pragma unroll 1
+        for (int sb = 0; sb < C::STEPS; sb += C::UNROLL) {
+          const uint32_t rb = rb_lane + sb * C::ROW_BYTES;
+          auto one_step = [&](auto uc) {
+            constexpr int u = decltype(uc)::value;
+            const int step = sb + u;
+            const unsigned long long codes = load_octet<BITS>(vc + step * (32 * BITS));
+            float v[8];
+            expand8<BITS, C::BOOKS, C::PRMT_ADDR, u * C::ROW_BYTES>(codes, rb, v);
 #pragma unroll
-        for (int h = 0; h < GQA; ++h) {
-          const float2 pp = w.pdup[t * GQA + h];
+            for (int h = 0; h < GQA; ++h) {
+              const float2 pp = pd[step * (2 * GQA) + h];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) ffma2(out2[j][h], make_float2(v[2 * j], v[2 * j + 1]), pp);
+              for (int j = 0; j < 4; ++j) ffma2(out2[j][h], make_float2(v[2 * j], v[2 * j + 1]), pp);
+            }
+          };
+          one_step(std::integral_constant<int, 0>{});
+          one_step(std::integral_constant<int, 1>{});
+          one_step(std::integral_constant<int, 2>{});
+          one_step(std::integral_constant<int, 3>{});
         }
       }
     } else {
@@ -553,6 +560,10 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
   int warps = (int)((budget - shared) / per_warp);
   if (warps < 1) return mz_fail(MZ_ERR_UNSUPPORTED, "tile does not fit shared memory");
   if (warps > 8) warps = 8;
+  if (const char* e = std::getenv("MZ_TILES_WARPS")) {   // tuning aid: fewer warps per CTA
+    const int w = atoi(e);
+    if (w >= 1 && w < warps) warps = w;
+  }
   t.warps_per_cta = warps;
   t.smem_per_warp = per_warp;
   t.smem_bytes = shared + per_warp * warps;
@@ -578,6 +589,11 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
 }
 
 int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st) {
+#ifdef MZ_TILES_HEADLINE_ONLY   // fast experimental builds: only the two headline shapes
+  if (p.s.group == 64 && p.gqa == 4 && p.s.bits == 4) return mzt::launch_one<4, 64, 4>(p, st);
+  if (p.s.group == 64 && p.gqa == 4 && p.s.bits == 2) return mzt::launch_one<2, 64, 4>(p, st);
+  return mz_fail(MZ_ERR_UNSUPPORTED, "experimental build");
+#else
   switch (p.s.bits) {
     case 1: return mzt::launch_group<1>(p, st);
     case 2: return mzt::launch_group<2>(p, st);
@@ -589,6 +605,7 @@ int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st) {
     case 8: return mzt::launch_group<8>(p, st);
   }
   return mz_fail(MZ_ERR_UNSUPPORTED, "bits %d", p.s.bits);
+#endif
 }
 
 int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t st) {

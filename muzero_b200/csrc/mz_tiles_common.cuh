@@ -17,6 +17,14 @@ struct Cfg {
   static constexpr int TILE_BYTES = D * QB;        // packed bytes of a key tile == of a value tile
   static constexpr bool BOOKS = BITS <= 4;         // per-row codebooks; wider codes are expanded arithmetically
   static constexpr int BOOK_STRIDE = !BOOKS ? 8 : NE;   // floats per row
+  static constexpr int STEPS = D / RPS;            // steps per tile side (keys: 128 rows / RPS; values: G/2 token pairs)
+  // expansion rows are stored [row % RPS][row / RPS][BOOK_STRIDE]: the rows one lane visits are
+  // contiguous, so a lookup address is lane_base + step*ROW_BYTES + code*4
+  static constexpr int ROW_BYTES = BOOK_STRIDE * 4;
+  static constexpr int LANE_BLOCK_BYTES = STEPS * ROW_BYTES;
+  static constexpr int UNROLL = 4;
+  // with 4-bit codes and 256-byte aligned bases the address of a lookup is one byte permute
+  static constexpr bool PRMT_ADDR = BITS == 4 && (LANE_BLOCK_BYTES % 256 == 0) && ((UNROLL * ROW_BYTES) % 256 == 0);
   static constexpr int ROUNDS = (GQA + RPS - 1) / RPS;  // softmax rounds: a lane owns head r*RPS+dl in round r
   static constexpr int META_BYTES = 1024;          // 2 x 128 entries x up to 4 bytes
   // per-warp shared memory, in bytes (every region 16-byte aligned)
@@ -26,10 +34,10 @@ struct Cfg {
   static constexpr int PDUP = G * GQA * 8;
   static constexpr int QDUP = D * GQA * 8;
   static constexpr int MISC = 64;
-  static constexpr int PER_WARP = KBUF + VBUF + BOOK_BYTES + PDUP + QDUP + MISC;
+  static constexpr int PER_WARP = ((KBUF + VBUF + BOOK_BYTES + PDUP + QDUP + MISC + 255) / 256) * 256;
   // per-CTA shared: two universal tables [NE][NE+1] float2 (keys, values)
   static constexpr int UNIV_FLOAT2 = BOOKS ? NE * (NE + 1) : 0;
-  static constexpr int SHARED = ((2 * UNIV_FLOAT2 * 8 + 15) / 16) * 16;
+  static constexpr int SHARED = ((2 * UNIV_FLOAT2 * 8 + 255) / 256) * 256 + 256;   // + slack to align the base to 256
 };
 
 // ---- asynchronous copies (global -> shared, 16 bytes per lane per call) ----
@@ -89,23 +97,52 @@ __device__ __forceinline__ unsigned long long load_octet(const uint8_t* p) {
   return v;
 }
 
-// 8 codes -> 8 values.  BOOKS: `row` is that row's codebook; otherwise its 8 parameters
-// {A, Bup, Bdn, kup, kdn, zero_code, -, -}: value = A + Bup*(2^(n*kup)-1) above the zero code,
-// A - Bdn*(2^(n*kdn)-1) below it.
-template <int BITS, bool BOOKS>
-__device__ __forceinline__ void expand8(unsigned long long codes, const float* __restrict__ row, float (&v)[8]) {
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+template <int IMM>
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ float4 lds_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr), "n"(IMM));
+  return v;
+}
+
+// 8 codes -> 8 values.  `rb` is the shared-window address of the lane's expansion rows for the
+// current unrolled block (aligned to 64 bytes, to 256 when PRMT is set); IMM selects the row.
+// BOOKS: the row is a codebook.  Otherwise it holds {A, Bup, Bdn, kup, kdn, zero_code, -, -}:
+// value = A + Bup*(2^(n*kup)-1) above the zero code, A - Bdn*(2^(n*kdn)-1) below it.
+template <int BITS, bool BOOKS, bool PRMT, int IMM>
+__device__ __forceinline__ void expand8(unsigned long long codes, uint32_t rb, float (&v)[8]) {
   constexpr unsigned MASK = (1u << BITS) - 1u;
   if (BOOKS) {
     const uint32_t c32 = (uint32_t)codes;   // BITS <= 4: all 8 codes fit 32 bits
+    if (PRMT) {
+      const uint32_t even = (c32 << 2) & 0x3C3C3C3Cu;   // byte j = 4 * code(2j)
+      const uint32_t odd = (c32 >> 2) & 0x3C3C3C3Cu;    // byte j = 4 * code(2j+1)
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const int sh = BITS * k - 2;
-      const uint32_t off = sh >= 0 ? ((c32 >> (sh >= 0 ? sh : 0)) & (MASK << 2)) : ((c32 << (sh < 0 ? -sh : 0)) & (MASK << 2));
-      v[k] = *(const float*)((const uint8_t*)row + off);
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = lds_f32<IMM>(prmt(even, rb, 0x7650u + j));
+        v[2 * j + 1] = lds_f32<IMM>(prmt(odd, rb, 0x7650u + j));
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int sh = BITS * k - 2;
+        const uint32_t off = sh >= 0 ? ((c32 >> (sh >= 0 ? sh : 0)) & (MASK << 2)) : ((c32 << (sh < 0 ? -sh : 0)) & (MASK << 2));
+        v[k] = lds_f32<IMM>(rb | off);
+      }
     }
   } else {
-    const float4 a = *(const float4*)row;
-    const float4 b = *(const float4*)(row + 4);
+    const float4 a = lds_f32x4<IMM>(rb);
+    const float4 b = lds_f32x4<IMM + 16>(rb);
     const int zc = __float_as_int(b.y);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
