@@ -163,6 +163,36 @@ size_t mz_decode_workspace_bytes(const mz_decode_args* args);
 int mz_decode_attention(const mz_decode_args* args, void* stream);
 
 /*
+ * Decode attention for callers that cannot allocate device memory.
+ * (No counterpart in the reference: its kernels always receive torch-allocated buffers.)
+ *
+ * Some hosts of this library may not call cudaMalloc at all once they are running: a serving
+ * process whose memory pool was carved up at start-up and hands out nothing afterwards, code
+ * that runs while a CUDA graph is being captured, or a plug-in loaded into a runtime that owns
+ * the allocator.  mz_decode_attention needs a caller-provided workspace for the per-split
+ * partial results; this variant keeps that scratch inside the library instead, in one
+ * file-scope device array of MZ_STATIC_SCRATCH_BYTES (8 MiB) that every GPU holds from the
+ * moment it loads the library until the process exits.
+ *
+ * Same arguments and result as mz_decode_attention; args->workspace and
+ * args->workspace_bytes are ignored.  The call itself makes no cudaMalloc / cudaFree and calls
+ * no allocating routine.  Limits and rules:
+ *   - the call is refused (MZ_ERR_WORKSPACE, with the sizes in the message) when the partial
+ *     results of the request do not fit MZ_STATIC_SCRATCH_BYTES;
+ *   - it is refused (MZ_ERR_UNSUPPORTED) for shapes that run on the shape-generic kernel,
+ *     because that kernel reads lookup tables which are allocated on first use;
+ *   - the first call on each device looks up the device address of the array
+ *     (cudaGetSymbolAddress, with that device current); make that first call outside any
+ *     stream capture;
+ *   - all calls on a device share the one array and it keeps the previous call's contents.
+ *     Nothing in it has to start at zero (every record a call reads it has written itself),
+ *     but two calls that overlap on the GPU - different streams, or different host threads -
+ *     race on it: serialise them on one stream.
+ */
+#define MZ_STATIC_SCRATCH_BYTES (8u << 20)
+int mz_decode_attention_static(const mz_decode_args* args, void* stream);
+
+/*
  * Same, but stops before normalisation: writes the merged partial triple of
  * this call's tokens, m[B,H], l[B,H], acc[B,H,D] (fp32).  Used when the KV
  * sequence is split across GPUs.  args->out is ignored.

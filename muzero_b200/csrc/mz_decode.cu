@@ -129,6 +129,17 @@ int finish(const Plan& plan, const MzDecodeOut& o, cudaStream_t st) {
 }
 }  // namespace
 
+// Internal (used by the static-scratch entry point): scratch bytes a call needs and whether it
+// would use the lazily allocated lookup tables.  Returns the validation status.
+int mz_decode_plan_info(const mz_decode_args* args, size_t* ws_bytes, int* needs_tables) {
+  Plan plan;
+  int rc = make_plan(args, &plan, false);
+  if (rc) return rc;
+  *ws_bytes = plan.ws_bytes;
+  *needs_tables = plan.tiles ? 0 : 1;
+  return MZ_OK;
+}
+
 extern "C" size_t mz_decode_workspace_bytes(const mz_decode_args* args) {
   Plan plan;
   if (make_plan(args, &plan, false) != MZ_OK) return 0;
