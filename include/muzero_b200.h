@@ -167,9 +167,9 @@ int mz_decode_attention(const mz_decode_args* args, void* stream);
  * (No counterpart in the reference: its kernels always receive torch-allocated buffers.)
  *
  * Some hosts of this library may not call cudaMalloc at all once they are running: a serving
- * process whose memory pool was carved up at start-up and hands out nothing afterwards, code
- * that runs while a CUDA graph is being captured, or a plug-in loaded into a runtime that owns
- * the allocator.  mz_decode_attention needs a caller-provided workspace for the per-split
+ * process whose memory pool was carved up at start-up and hands out nothing afterwards, a
+ * latency-critical decode loop that forbids cudaMalloc because it synchronises the device, or a
+ * plug-in loaded into a runtime that owns the allocator.  mz_decode_attention needs a caller-provided workspace for the per-split
  * partial results; this variant keeps that scratch inside the library instead, in one
  * file-scope device array of MZ_STATIC_SCRATCH_BYTES (8 MiB) that every GPU holds from the
  * moment it loads the library until the process exits.

@@ -1,8 +1,9 @@
 """GPU: the allocation-free decode entry point (``mz_decode_attention_static``).
 
 Some users of this library cannot allocate device memory when they call it - a serving
-process that handed its whole memory pool out at start-up, code running under stream capture,
-a plug-in inside a runtime that owns the allocator.  For them the library keeps the scratch of
+process that handed its whole memory pool out at start-up, a latency-critical decode loop that
+forbids cudaMalloc because it synchronises the device, a plug-in inside a runtime that owns the
+allocator.  For them the library keeps the scratch of
 the decode attention in a static 8 MiB device array.  This test drives the entry point through
 the C ABI, twice in a row on different inputs (the array is shared and keeps old contents),
 and checks each result against the ordinary entry point (same kernels, so the tolerance the
