@@ -263,6 +263,37 @@ def run_ours(args) -> dict:
     return result if rank == 0 else {}
 
 
+def run_attention_only(args) -> dict:
+    """Small standalone case for profilers: `--layers` caches of `--batch` sequences, `--steps`
+    rounds of one fused decode-attention call per cache, nothing else on the GPU."""
+    from muzero_b200.cache.attention import build_decode_args
+    from muzero_b200.kernels.loader import load_mu_zero_cuda_extension
+    from muzero_b200.kernels._cabi import stream_ptr
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    layers = build_layers(args.bits, device, args.layers, args.batch, seed=1234)
+    q = torch.randn(args.batch, QH, 1, D, device=device).to(torch.bfloat16)
+    outs = [torch.empty(args.batch, 1, QH, D, dtype=torch.bfloat16, device=device) for _ in layers]
+    cargs = [build_decode_args(l, q, D ** -0.5, None, o) for l, o in zip(layers, outs)]
+    lib, st = load_mu_zero_cuda_extension(), stream_ptr(device)
+    for _ in range(args.warmup):
+        for a in cargs:
+            lib.mz_decode_attention(ctypes.byref(a), st)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        for a in cargs:
+            lib.mz_decode_attention(ctypes.byref(a), st)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * len(cargs))
+    abytes = algorithmic_bytes(args.bits, batch=args.batch)
+    peak, kind = measured_peak_gbs()
+    return {"mode": "attention-only", "bits": args.bits, "batch": args.batch, "layers": args.layers, "us_per_call": us,
+            "bytes_per_call": abytes, "achieved_gbs": abytes / us / 1e3, "frac_of_peak": abytes / us / 1e3 / peak, "peak_kind": kind}
+
+
 def cpu_baseline(bits: int, seconds: float) -> dict:
     """The oracle (CPU restatement of the reference's torch path) on a bounded sample of the workload."""
     import importlib.util
@@ -323,8 +354,12 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--attention-only", action="store_true", help="small profiling case: only the fused attention calls")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.attention_only:
+        print(json.dumps(run_attention_only(args)))
+        return
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out:
         print(json.dumps(out))

@@ -19,14 +19,14 @@ namespace mzt {
 template <int BITS, int G, int GQA>
 struct Warp {
   using C = Cfg<BITS, G, GQA>;
-  uint8_t* kbuf; uint8_t* vbuf;
-  float* books; float2* pdup; float2* qdup; float* corr;
+  float* books; uint8_t* kbuf; uint8_t* vbuf;
+  float* pbuf; float* qbuf; float* corr;
   const float2* univ_k; const float2* univ_v;
-  int lane, o, dl;        // key phase: o = octet of tokens, dl = row within a step
-  int vt, vj;             // value phase: token parity within a step, octet of channels
+  int lane, dl, q16;      // key phase: half-warp (row parity) and token slot within the row
 };
 
-// ---- per-row expansion data for one staged tile side (keys: 128 channel rows; values: G*NG rows)
+// ---- per-row expansion data for one staged tile side (128 rows), row r at r * ROW_BYTES: rows
+// that one lookup instruction touches together (r, r+1) then sit in different bank halves.
 template <int BITS, int G, int GQA>
 __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const uint8_t* meta, int meta_dt, const float2* univ,
                                            float alpha, float lg2a) {
@@ -34,6 +34,8 @@ __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const ui
   constexpr int TOP = C::NE - 1;
   const uint8_t* lo_p = meta;
   const uint8_t* sp_p = meta + C::META_BYTES / 2;
+  // rotation of the 4-entry store groups that makes the 16-byte stores of 8 neighbouring lanes hit 8 bank groups
+  const int rot = (w.lane >> 1) & 3;
 #pragma unroll
   for (int i = 0; i < D / 32; ++i) {
     const int r = w.lane + 32 * i;
@@ -47,10 +49,21 @@ __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const ui
     const float A = fmaf(span, anchor, lo);
     const float Bup = span * fmaxf(1.0f - anchor, 1e-8f);
     const float Bdn = span * fmaxf(anchor, 1e-8f);
-    float* dst = w.books + ((r % C::RPS) * C::STEPS + r / C::RPS) * C::BOOK_STRIDE;
+    float* dst = w.books + r * C::BOOK_STRIDE;
     if (C::BOOKS) {
       const float2* u = univ + zc * (C::NE + 1);
-      if (C::NE >= 4) {
+      if (C::NE >= 16) {
+#pragma unroll
+        for (int g = 0; g < C::NE / 4; ++g) {
+          const int e = ((g + rot) & (C::NE / 4 - 1)) * 4;
+          float4 o4;
+          o4.x = fmaf(Bdn, u[e].y, fmaf(Bup, u[e].x, A));
+          o4.y = fmaf(Bdn, u[e + 1].y, fmaf(Bup, u[e + 1].x, A));
+          o4.z = fmaf(Bdn, u[e + 2].y, fmaf(Bup, u[e + 2].x, A));
+          o4.w = fmaf(Bdn, u[e + 3].y, fmaf(Bup, u[e + 3].x, A));
+          *(float4*)(dst + e) = o4;
+        }
+      } else if (C::NE >= 4) {
 #pragma unroll
         for (int e = 0; e < C::NE; e += 4) {
           float4 o4;
@@ -73,44 +86,44 @@ __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const ui
   }
 }
 
-// ---- online softmax over one tile.  s[r][k]: base-2 logits of this lane's 8 tokens for the
-// head it owns in round r (head = r*RPS + dl).  Writes p pairs to pdup and corrections to corr.
+// ---- online softmax over one tile.  s[r][k]: base-2 logits of this lane's TPL tokens for the
+// head it owns in round r (head = 2*r + dl).  Writes probabilities to pbuf and corrections to corr.
 template <int BITS, int G, int GQA>
-__device__ __forceinline__ void softmax_tile(const Warp<BITS, G, GQA>& w, float (&s)[Cfg<BITS, G, GQA>::ROUNDS][8],
+__device__ __forceinline__ void softmax_tile(const Warp<BITS, G, GQA>& w, float (&s)[Cfg<BITS, G, GQA>::ROUNDS][Cfg<BITS, G, GQA>::TPL],
                                              float (&m_st)[Cfg<BITS, G, GQA>::ROUNDS], float (&l_st)[Cfg<BITS, G, GQA>::ROUNDS]) {
   using C = Cfg<BITS, G, GQA>;
 #pragma unroll
   for (int r = 0; r < C::ROUNDS; ++r) {
-    const int h = r * C::RPS + w.dl;
+    const int h = 2 * r + w.dl;
     float mx = s[r][0];
 #pragma unroll
-    for (int k = 1; k < 8; ++k) mx = fmaxf(mx, s[r][k]);
+    for (int k = 1; k < C::TPL; ++k) mx = fmaxf(mx, s[r][k]);
 #pragma unroll
-    for (int off = 1; off < C::LPR; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    for (int off = 1; off < 16; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     const float m_new = fmaxf(m_st[r], mx);
     const bool dead = !(m_new > -INFINITY);
     float sum = 0.f;
-    float pr[8];
+    float pr[C::TPL];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
+    for (int k = 0; k < C::TPL; ++k) {
       pr[k] = dead ? 0.f : ex2f(s[r][k] - m_new);
       sum += pr[k];
     }
 #pragma unroll
-    for (int off = 1; off < C::LPR; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    for (int off = 1; off < 16; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
     const float c = dead ? 1.0f : ex2f(m_st[r] - m_new);   // m_st = -inf -> 0
     l_st[r] = l_st[r] * c + sum;
     m_st[r] = m_new;
     if (h < GQA) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) w.pdup[(w.o * 8 + k) * GQA + h] = make_float2(pr[k], pr[k]);
-      if (w.o == 0) w.corr[h] = c;
+      for (int k = 0; k < C::TPL; ++k) w.pbuf[(w.q16 * C::TPL + k) * GQA + h] = pr[k];
+      if (w.q16 == 0) w.corr[h] = c;
     }
   }
 }
 
 template <int BITS, int G, int GQA>
-__global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodeParams p) {
+__global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodeParams p) {
   using C = Cfg<BITS, G, GQA>;
   extern __shared__ __align__(16) uint8_t smem[];
   const mz_kv_store& s = p.s;
@@ -152,16 +165,16 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
   w.books = (float*)base;
   w.kbuf = base + C::BOOK_BYTES;
   w.vbuf = w.kbuf + C::KBUF;
-  w.pdup = (float2*)(w.vbuf + C::VBUF);
-  w.qdup = (float2*)((uint8_t*)w.pdup + C::PDUP);
-  w.corr = (float*)((uint8_t*)w.qdup + C::QDUP);
+  w.pbuf = (float*)(w.vbuf + C::VBUF);
+  w.qbuf = (float*)((uint8_t*)w.pbuf + C::PBUF);
+  w.corr = (float*)((uint8_t*)w.qbuf + C::QBUF);
   w.univ_k = univ_k; w.univ_v = univ_v;
-  w.lane = lane; w.o = lane % C::LPR; w.dl = lane / C::LPR;
-  w.vt = lane >> 4; w.vj = lane & 15;
+  w.lane = lane; w.dl = lane >> 4; w.q16 = lane & 15;
 
   const int msz = s.meta_dtype == MZ_F32 ? 4 : 2;
   const float lg2a_k = log2f(1.0f + s.alpha_key), lg2a_v = log2f(1.0f + s.alpha_value);
   const int nq = s.k_groups * G;
+  const uint32_t books_sa = (uint32_t)__cvta_generic_to_shared(w.books);
 
   auto stage_k = [&](long long f) {
     if (f < f1) {
@@ -192,13 +205,13 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
     cp_async_commit();
   };
 
-  float2 out2[4][GQA];
+  float2 out2[2][GQA];               // this lane's 4 channels (4*lane ..) as two pairs, per head
   float m_st[C::ROUNDS], l_st[C::ROUNDS];
   int cur_pair = -1, seg = 0;
 
   auto reset_state = [&]() {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int h = 0; h < GQA; ++h) out2[j][h] = make_float2(0.f, 0.f);
 #pragma unroll
@@ -207,23 +220,12 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
   auto write_partial = [&]() {
     const long long slot0 = ((long long)gw * p.tp.max_segs + seg) * GQA;
 #pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      float2 t[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        t[j].x = out2[j][h].x + __shfl_xor_sync(0xffffffffu, out2[j][h].x, 16);
-        t[j].y = out2[j][h].y + __shfl_xor_sync(0xffffffffu, out2[j][h].y, 16);
-      }
-      if (lane < 16) {
-        float4* dst = (float4*)(p.part.acc + (slot0 + h) * D + lane * 8);
-        dst[0] = make_float4(t[0].x, t[0].y, t[1].x, t[1].y);
-        dst[1] = make_float4(t[2].x, t[2].y, t[3].x, t[3].y);
-      }
-    }
+    for (int h = 0; h < GQA; ++h)
+      *(float4*)(p.part.acc + (slot0 + h) * D + lane * 4) = make_float4(out2[0][h].x, out2[0][h].y, out2[1][h].x, out2[1][h].y);
 #pragma unroll
     for (int r = 0; r < C::ROUNDS; ++r) {
-      const int h = r * C::RPS + w.dl;
-      if (h < GQA && w.o == 0) {
+      const int h = 2 * r + w.dl;
+      if (h < GQA && w.q16 == 0) {
         p.part.m[slot0 + h] = m_st[r] * (1.0f / LOG2E);   // back to natural-log units
         p.part.l[slot0 + h] = l_st[r];
       }
@@ -243,8 +245,7 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
       const float qs = p.scaling * LOG2E;
       for (int i = lane; i < D * GQA; i += 32) {
         const int d = i / GQA, h = i % GQA;
-        const float q = mz_load_as_float(p.query, b * p.q_stride_b + (long long)(kvh * GQA + h) * p.q_stride_h + d, s.kv_dtype) * qs;
-        w.qdup[i] = make_float2(q, q);
+        w.qbuf[i] = mz_load_as_float(p.query, b * p.q_stride_b + (long long)(kvh * GQA + h) * p.q_stride_h + d, s.kv_dtype) * qs;
       }
       __syncwarp();
     }
@@ -252,37 +253,48 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
     const int tok0 = dense ? (tile - s.k_groups) * G : tile * G;      // first token inside its region
     const int ntok = dense ? min(G, s.res_len - tok0) : G;
     const long long mask0 = p.mask ? b * p.mask_stride_b + (dense ? nq : 0) + tok0 : 0;
-    float sl[C::ROUNDS][8];
+    float sl[C::ROUNDS][C::TPL];
 
     cp_async_wait<1>();
     __syncwarp();
     if (!dense) {
-      // ---------------- keys: expansion data, then QK with all heads per code
+      // ---------------- keys: expansion rows, then QK with all heads per code
       build_rows<BITS, G, GQA>(w, w.kbuf + C::TILE_BYTES, s.meta_dtype, w.univ_k, s.alpha_key, lg2a_k);
       __syncwarp();
-      float2 acc[4][GQA];
+      float2 acc2[C::TPL / 2][GQA];      // token pairs (2j, 2j+1)
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int k = 0; k < C::TPL / 2; ++k)
 #pragma unroll
-        for (int h = 0; h < GQA; ++h) acc[j][h] = make_float2(0.f, 0.f);
+        for (int h = 0; h < GQA; ++h) acc2[k][h] = make_float2(0.f, 0.f);
       {
-        const uint32_t rb_lane = (uint32_t)__cvta_generic_to_shared(w.books) + w.dl * C::LANE_BLOCK_BYTES;
-        const uint8_t* kc = w.kbuf + w.dl * C::QB + w.o * BITS;
-        const float2* qd = w.qdup + w.dl * GQA;
+        const uint32_t lane_off = w.dl * C::ROW_BYTES;        // row 2*step + dl
+        const uint8_t* krow = w.kbuf + w.dl * C::QB;
+        const float* qd = w.qbuf + w.dl * GQA;
 #pragma unroll 1
-        for (int sb = 0; sb < C::STEPS; sb += C::UNROLL) {
-          const uint32_t rb = rb_lane + sb * C::ROW_BYTES;
+        for (int sb = 0; sb < C::KSTEPS; sb += C::UNROLL) {
+          const uint32_t rb = books_sa + sb * (2 * C::ROW_BYTES);
           auto one_step = [&](auto uc) {
             constexpr int u = decltype(uc)::value;
             const int step = sb + u;
-            const unsigned long long codes = load_octet<BITS>(kc + step * (C::RPS * C::QB));
-            float v[8];
-            expand8<BITS, C::BOOKS, C::PRMT_ADDR, u * C::ROW_BYTES>(codes, rb, v);
+            const unsigned long long codes = load_codes<BITS, C::TPL>(krow + step * (2 * C::QB), w.q16 * C::TPL);
+            float v[C::TPL];
+            expand<BITS, C::BOOKS, C::PRMT_ADDR, C::TPL, u * (2 * C::ROW_BYTES)>(codes, rb, lane_off, v);
+            float qh[GQA];
+            if (GQA % 4 == 0) {
+#pragma unroll
+              for (int h = 0; h < GQA; h += 4) {
+                const float4 t4 = *(const float4*)(qd + step * (2 * GQA) + h);
+                qh[h] = t4.x; qh[h + 1] = t4.y; qh[h + 2] = t4.z; qh[h + 3] = t4.w;
+              }
+            } else {
+#pragma unroll
+              for (int h = 0; h < GQA; ++h) qh[h] = qd[step * (2 * GQA) + h];
+            }
 #pragma unroll
             for (int h = 0; h < GQA; ++h) {
-              const float2 qq = qd[step * (C::RPS * GQA) + h];
+              const float2 qq = make_float2(qh[h], qh[h]);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) ffma2(acc[j][h], make_float2(v[2 * j], v[2 * j + 1]), qq);
+              for (int k = 0; k < C::TPL; k += 2) ffma2(acc2[k / 2][h], make_float2(v[k], v[k + 1]), qq);
             }
           };
           one_step(std::integral_constant<int, 0>{});
@@ -291,29 +303,27 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
           one_step(std::integral_constant<int, 3>{});
         }
       }
-      // sum over the rows handled by the other lanes of this token octet
+      // add the rows handled by the other half-warp
 #pragma unroll
-      for (int off = C::LPR; off < 32; off <<= 1)
+      for (int k = 0; k < C::TPL / 2; ++k)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int h = 0; h < GQA; ++h) {
-            acc[j][h].x += __shfl_xor_sync(0xffffffffu, acc[j][h].x, off);
-            acc[j][h].y += __shfl_xor_sync(0xffffffffu, acc[j][h].y, off);
-          }
+        for (int h = 0; h < GQA; ++h) {
+          acc2[k][h].x += __shfl_xor_sync(0xffffffffu, acc2[k][h].x, 16);
+          acc2[k][h].y += __shfl_xor_sync(0xffffffffu, acc2[k][h].y, 16);
+        }
 #pragma unroll
       for (int r = 0; r < C::ROUNDS; ++r)
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < C::TPL; ++k) {
           float val = 0.f;
 #pragma unroll
           for (int h = 0; h < GQA; ++h)
-            if (h / C::RPS == r && h % C::RPS == w.dl) val = (k & 1) ? acc[k >> 1][h].y : acc[k >> 1][h].x;
+            if (h / 2 == r && (h & 1) == w.dl) val = (k & 1) ? acc2[k / 2][h].y : acc2[k / 2][h].x;
           sl[r][k] = val;
         }
     } else {
       // ---------------- dense residual keys: one token per lane, logits exchanged through shared memory
-      float* sbuf = (float*)w.pdup;
+      float* sbuf = w.pbuf;
       const uint16_t* rk = (const uint16_t*)s.res_k + b * s.res_stride_b + kvh * s.res_stride_h;
 #pragma unroll 1
       for (int i = 0; i < G / 32; ++i) {
@@ -333,8 +343,8 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
               const int d = c * 8 + 2 * e;
 #pragma unroll
               for (int h = 0; h < GQA; ++h) {
-                dot[h] = fmaf(x.x, w.qdup[d * GQA + h].x, dot[h]);
-                dot[h] = fmaf(x.y, w.qdup[(d + 1) * GQA + h].x, dot[h]);
+                dot[h] = fmaf(x.x, w.qbuf[d * GQA + h], dot[h]);
+                dot[h] = fmaf(x.y, w.qbuf[(d + 1) * GQA + h], dot[h]);
               }
             }
           }
@@ -345,17 +355,17 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
       __syncwarp();
 #pragma unroll
       for (int r = 0; r < C::ROUNDS; ++r) {
-        const int h = min(r * C::RPS + w.dl, GQA - 1);
+        const int h = min(2 * r + w.dl, GQA - 1);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) sl[r][k] = sbuf[(w.o * 8 + k) * GQA + h];
+        for (int k = 0; k < C::TPL; ++k) sl[r][k] = sbuf[(w.q16 * C::TPL + k) * GQA + h];
       }
     }
-    __syncwarp();                 // every lane is done with kbuf, books and sbuf
+    __syncwarp();                 // every lane is done with kbuf, the rows and sbuf
     stage_k(f + 1);
     if (p.mask) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int t = w.o * 8 + k;
+      for (int k = 0; k < C::TPL; ++k) {
+        const int t = w.q16 * C::TPL + k;
         const float mv = t < ntok ? mz_load_as_float(p.mask, mask0 + t, p.mask_dtype) * LOG2E : 0.f;
 #pragma unroll
         for (int r = 0; r < C::ROUNDS; ++r) sl[r][k] += mv;
@@ -363,7 +373,7 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
     }
     softmax_tile<BITS, G, GQA>(w, sl, m_st, l_st);
     cp_async_wait<1>();
-    __syncwarp();                 // value tile landed; p pairs and corrections visible
+    __syncwarp();                 // value tile landed; probabilities and corrections visible
     {
       bool rescale = false;
       float cr[GQA];
@@ -371,7 +381,7 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
       for (int h = 0; h < GQA; ++h) { cr[h] = w.corr[h]; rescale |= cr[h] != 1.0f; }
       if (rescale) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int h = 0; h < GQA; ++h) { out2[j][h].x *= cr[h]; out2[j][h].y *= cr[h]; }
       }
@@ -380,24 +390,33 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
       build_rows<BITS, G, GQA>(w, w.vbuf + C::TILE_BYTES, s.meta_dtype, w.univ_v, s.alpha_value, lg2a_v);
       __syncwarp();
       {
-        const int lane_row = w.vt * C::NG + (w.vj * 8) / G;
-        const uint32_t rb_lane = (uint32_t)__cvta_generic_to_shared(w.books) + lane_row * C::LANE_BLOCK_BYTES;
-        const uint8_t* vc = w.vbuf + w.vt * (16 * BITS) + w.vj * BITS;
-        const float2* pd = w.pdup + w.vt * GQA;
+        const int grp = (lane * 4) / G;
+        const uint32_t lane_off = grp * C::ROW_BYTES;         // row t*NG + grp
 #pragma unroll 1
-        for (int sb = 0; sb < C::STEPS; sb += C::UNROLL) {
-          const uint32_t rb = rb_lane + sb * C::ROW_BYTES;
+        for (int sb = 0; sb < C::VSTEPS; sb += C::UNROLL) {
+          const uint32_t rb = books_sa + sb * (C::NG * C::ROW_BYTES);
           auto one_step = [&](auto uc) {
             constexpr int u = decltype(uc)::value;
-            const int step = sb + u;
-            const unsigned long long codes = load_octet<BITS>(vc + step * (32 * BITS));
-            float v[8];
-            expand8<BITS, C::BOOKS, C::PRMT_ADDR, u * C::ROW_BYTES>(codes, rb, v);
+            const int t = sb + u;
+            const unsigned long long codes = load_codes<BITS, 4>(w.vbuf + t * C::VROW_BYTES, lane * 4);
+            float v[4];
+            expand<BITS, C::BOOKS, C::PRMT_ADDR, 4, u * (C::NG * C::ROW_BYTES)>(codes, rb, lane_off, v);
+            float ph[GQA];
+            if (GQA % 4 == 0) {
+#pragma unroll
+              for (int h = 0; h < GQA; h += 4) {
+                const float4 t4 = *(const float4*)(w.pbuf + t * GQA + h);
+                ph[h] = t4.x; ph[h + 1] = t4.y; ph[h + 2] = t4.z; ph[h + 3] = t4.w;
+              }
+            } else {
+#pragma unroll
+              for (int h = 0; h < GQA; ++h) ph[h] = w.pbuf[t * GQA + h];
+            }
 #pragma unroll
             for (int h = 0; h < GQA; ++h) {
-              const float2 pp = pd[step * (2 * GQA) + h];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) ffma2(out2[j][h], make_float2(v[2 * j], v[2 * j + 1]), pp);
+              const float2 pp = make_float2(ph[h], ph[h]);
+              ffma2(out2[0][h], make_float2(v[0], v[1]), pp);
+              ffma2(out2[1][h], make_float2(v[2], v[3]), pp);
             }
           };
           one_step(std::integral_constant<int, 0>{});
@@ -407,23 +426,21 @@ __global__ void __launch_bounds__(256, 1) decode_tiles_kernel(const MzDecodePara
         }
       }
     } else {
-      const uint16_t* rv = (const uint16_t*)s.res_v + b * s.res_stride_b + kvh * s.res_stride_h + w.vj * 8;
-#pragma unroll 2
-      for (int step = 0; step < G / 2; ++step) {
-        const int t = 2 * step + w.vt;
-        if (t < ntok) {
-          const uint4 raw = __ldg((const uint4*)(rv + (long long)(s.res_start + tok0 + t) * s.res_stride_t));
-          const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+      const uint16_t* rv = (const uint16_t*)s.res_v + b * s.res_stride_b + kvh * s.res_stride_h + lane * 4;
+#pragma unroll 4
+      for (int t = 0; t < ntok; ++t) {
+        const uint2 raw = __ldg((const uint2*)(rv + (long long)(s.res_start + tok0 + t) * s.res_stride_t));
+        const float2 x0 = unpack2(raw.x, s.kv_dtype), x1 = unpack2(raw.y, s.kv_dtype);
 #pragma unroll
-          for (int h = 0; h < GQA; ++h) {
-            const float2 pp = w.pdup[t * GQA + h];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) ffma2(out2[j][h], unpack2(ww[j], s.kv_dtype), pp);
-          }
+        for (int h = 0; h < GQA; ++h) {
+          const float ph = w.pbuf[t * GQA + h];
+          const float2 pp = make_float2(ph, ph);
+          ffma2(out2[0][h], x0, pp);
+          ffma2(out2[1][h], x1, pp);
         }
       }
     }
-    __syncwarp();                 // every lane is done with vbuf, books and pdup
+    __syncwarp();                 // every lane is done with vbuf, the rows and pbuf
     stage_v(f + 1);
   }
   cp_async_wait<0>();
@@ -559,7 +576,7 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
   const unsigned budget = 220 * 1024;
   int warps = (int)((budget - shared) / per_warp);
   if (warps < 1) return mz_fail(MZ_ERR_UNSUPPORTED, "tile does not fit shared memory");
-  if (warps > 8) warps = 8;
+  if (warps > 12) warps = 12;
   if (const char* e = std::getenv("MZ_TILES_WARPS")) {   // tuning aid: fewer warps per CTA
     const int w = atoi(e);
     if (w >= 1 && w < warps) warps = w;

@@ -7,37 +7,41 @@ namespace mzt {
 constexpr int D = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// Lane mappings (one warp per tile of G tokens):
+//   keys   : 16 lanes share a row (one channel, G tokens), each lane owns TPL = G/16 consecutive
+//            tokens; the two half-warps take rows 2*step and 2*step+1            -> 64 steps
+//   values : 32 lanes share a token, each lane owns 4 consecutive channels       -> G steps
+// so one shared-memory lookup instruction touches at most two codebooks (keys) / NG codebooks
+// (values): with 16-entry books two of them cover the 32 banks exactly once, no conflicts.
 template <int BITS, int G, int GQA>
 struct Cfg {
   static constexpr int NE = 1 << BITS;             // codebook entries
   static constexpr int QB = G * BITS / 8;          // packed bytes of one row of G codes
-  static constexpr int LPR = G / 8;                // lanes that share one key row (8 tokens each)
-  static constexpr int RPS = 32 / LPR;             // key rows a warp covers per step
+  static constexpr int TPL = G / 16;               // tokens per lane per key row
   static constexpr int NG = D / G;                 // value groups per token
+  static constexpr int VROW_BYTES = 16 * BITS;     // packed bytes of one token's 128 value codes
   static constexpr int TILE_BYTES = D * QB;        // packed bytes of a key tile == of a value tile
   static constexpr bool BOOKS = BITS <= 4;         // per-row codebooks; wider codes are expanded arithmetically
-  static constexpr int BOOK_STRIDE = !BOOKS ? 8 : NE;   // floats per row
-  static constexpr int STEPS = D / RPS;            // steps per tile side (keys: 128 rows / RPS; values: G/2 token pairs)
-  // expansion rows are stored [row % RPS][row / RPS][BOOK_STRIDE]: the rows one lane visits are
-  // contiguous, so a lookup address is lane_base + step*ROW_BYTES + code*4
+  static constexpr int BOOK_STRIDE = !BOOKS ? 8 : (NE < 4 ? 4 : NE);   // floats per row
   static constexpr int ROW_BYTES = BOOK_STRIDE * 4;
-  static constexpr int LANE_BLOCK_BYTES = STEPS * ROW_BYTES;
+  static constexpr int KSTEPS = D / 2;             // key steps per tile
+  static constexpr int VSTEPS = G;                 // value steps per tile
   static constexpr int UNROLL = 4;
-  // with 4-bit codes and 256-byte aligned bases the address of a lookup is one byte permute
-  static constexpr bool PRMT_ADDR = BITS == 4 && (LANE_BLOCK_BYTES % 256 == 0) && ((UNROLL * ROW_BYTES) % 256 == 0);
-  static constexpr int ROUNDS = (GQA + RPS - 1) / RPS;  // softmax rounds: a lane owns head r*RPS+dl in round r
+  static constexpr int ROUNDS = (GQA + 1) / 2;     // softmax rounds: half-warp dl owns head 2*r + dl in round r
   static constexpr int META_BYTES = 1024;          // 2 x 128 entries x up to 4 bytes
-  // per-warp shared memory, in bytes (every region 16-byte aligned)
+  // 4-bit codes, 256-byte aligned lane blocks: the address of a lookup is one byte permute
+  static constexpr bool PRMT_ADDR = BITS == 4;
+  // per-warp shared memory, in bytes
+  static constexpr int BOOK_BYTES = D * ROW_BYTES;
   static constexpr int KBUF = TILE_BYTES + META_BYTES;
   static constexpr int VBUF = TILE_BYTES + META_BYTES;
-  static constexpr int BOOK_BYTES = D * BOOK_STRIDE * 4;
-  static constexpr int PDUP = G * GQA * 8;
-  static constexpr int QDUP = D * GQA * 8;
+  static constexpr int PBUF = G * GQA * 4;         // probabilities [token][head]; also dense-key logits
+  static constexpr int QBUF = D * GQA * 4;         // scaled query [channel][head]
   static constexpr int MISC = 64;
-  static constexpr int PER_WARP = ((KBUF + VBUF + BOOK_BYTES + PDUP + QDUP + MISC + 255) / 256) * 256;
-  // per-CTA shared: two universal tables [NE][NE+1] float2 (keys, values)
+  static constexpr int PER_WARP = ((BOOK_BYTES + KBUF + VBUF + PBUF + QBUF + MISC + 255) / 256) * 256;
+  // per-CTA shared: two universal tables [NE][NE+1] float2 (keys, values) + slack to align to 256
   static constexpr int UNIV_FLOAT2 = BOOKS ? NE * (NE + 1) : 0;
-  static constexpr int SHARED = ((2 * UNIV_FLOAT2 * 8 + 255) / 256) * 256 + 256;   // + slack to align the base to 256
+  static constexpr int SHARED = ((2 * UNIV_FLOAT2 * 8 + 255) / 256) * 256 + 256;
 };
 
 // ---- asynchronous copies (global -> shared, 16 bytes per lane per call) ----
@@ -54,7 +58,7 @@ __device__ __forceinline__ void warp_copy_async(uint8_t* dst, const uint8_t* src
   for (int off = lane * 16; off < bytes; off += 512) cp_async16(dst + off, src + off);
 }
 
-// ---- packed fp32 pairs: d += a * b on both halves (one issue slot on sm_100) ----
+// packed fp32 pair: d += a * b on both halves (one issue slot on sm_100)
 __device__ __forceinline__ void ffma2(float2& d, const float2 a, const float2 b) {
 #if defined(MZ_NO_F32X2)
   d.x = fmaf(a.x, b.x, d.x);
@@ -80,23 +84,6 @@ __device__ __forceinline__ float meta_at(const uint8_t* base, int i, int dt) {
   return mz_u16_to_float(((const uint16_t*)base)[i], dt);
 }
 
-// the BITS bytes that hold 8 consecutive codes, from shared memory
-template <int BITS>
-__device__ __forceinline__ unsigned long long load_octet(const uint8_t* p) {
-  if (BITS == 4) return *(const uint32_t*)p;
-  if (BITS == 8) return *(const unsigned long long*)p;
-  if (BITS == 2) return *(const uint16_t*)p;
-  if (BITS == 1) return *p;
-  if (BITS == 6) {
-    const uint16_t* q = (const uint16_t*)p;
-    return (unsigned long long)q[0] | ((unsigned long long)q[1] << 16) | ((unsigned long long)q[2] << 32);
-  }
-  unsigned long long v = 0;
-#pragma unroll
-  for (int i = 0; i < BITS; ++i) v |= ((unsigned long long)p[i]) << (8 * i);
-  return v;
-}
-
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t d;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
@@ -115,37 +102,62 @@ __device__ __forceinline__ float4 lds_f32x4(uint32_t addr) {
   return v;
 }
 
-// 8 codes -> 8 values.  `rb` is the shared-window address of the lane's expansion rows for the
-// current unrolled block (aligned to 64 bytes, to 256 when PRMT is set); IMM selects the row.
+// N consecutive codes of BITS bits starting at code index `first` of the packed row at `row`
+// (shared memory, 4-byte aligned); returned LSB-first in up to 64 bits.
+template <int BITS, int N>
+__device__ __forceinline__ unsigned long long load_codes(const uint8_t* row, int first) {
+  constexpr int NB = BITS * N;                      // bits wanted
+  if (NB == 8) return row[first * BITS >> 3];
+  if (NB == 16) return *(const uint16_t*)(row + (first * BITS >> 3));
+  if (NB == 32) return *(const uint32_t*)(row + (first * BITS >> 3));
+  if (NB == 64) return *(const unsigned long long*)(row + (first * BITS >> 3));
+  const int bit = first * BITS;
+  const uint32_t* w = (const uint32_t*)row + (bit >> 5);
+  const int sh = bit & 31;
+  if (NB <= 32) {
+    const uint32_t lo = w[0], hi = (sh + NB > 32) ? w[1] : 0u;
+    return __funnelshift_r(lo, hi, sh) & (NB == 32 ? 0xffffffffu : ((1u << (NB & 31)) - 1u));
+  }
+  const unsigned long long a = (unsigned long long)w[0] | ((unsigned long long)w[1] << 32);
+  const unsigned long long b = (sh + NB > 64) ? (unsigned long long)w[2] : 0ull;
+  unsigned long long v = a >> sh;
+  if (sh) v |= b << (64 - sh);
+  return NB == 64 ? v : (v & ((1ull << (NB & 63)) - 1ull));
+}
+
+// N codes -> N values.  `rb` is the shared-window address of the expansion rows of the current
+// unrolled block (256-byte aligned), `lane_off` (< 256, multiple of ROW_BYTES) the byte offset of
+// this lane's row inside a step, IMM the byte offset of the step.
 // BOOKS: the row is a codebook.  Otherwise it holds {A, Bup, Bdn, kup, kdn, zero_code, -, -}:
 // value = A + Bup*(2^(n*kup)-1) above the zero code, A - Bdn*(2^(n*kdn)-1) below it.
-template <int BITS, bool BOOKS, bool PRMT, int IMM>
-__device__ __forceinline__ void expand8(unsigned long long codes, uint32_t rb, float (&v)[8]) {
+template <int BITS, bool BOOKS, bool PRMT, int N, int IMM>
+__device__ __forceinline__ void expand(unsigned long long codes, uint32_t rb, uint32_t lane_off, float (&v)[N]) {
   constexpr unsigned MASK = (1u << BITS) - 1u;
   if (BOOKS) {
-    const uint32_t c32 = (uint32_t)codes;   // BITS <= 4: all 8 codes fit 32 bits
-    if (PRMT) {
-      const uint32_t even = (c32 << 2) & 0x3C3C3C3Cu;   // byte j = 4 * code(2j)
-      const uint32_t odd = (c32 >> 2) & 0x3C3C3C3Cu;    // byte j = 4 * code(2j+1)
+    const uint32_t c32 = (uint32_t)codes;   // BITS <= 4, N <= 8: all codes fit 32 bits
+    if (PRMT && (N % 2 == 0)) {
+      const uint32_t lo4 = lane_off * 0x01010101u;      // lane_off in every byte
+      const uint32_t even = ((c32 << 2) & 0x3C3C3C3Cu) | lo4;   // byte j = 4 * code(2j) + lane_off
+      const uint32_t odd = ((c32 >> 2) & 0x3C3C3C3Cu) | lo4;    // byte j = 4 * code(2j+1) + lane_off
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < N / 2; ++j) {
         v[2 * j] = lds_f32<IMM>(prmt(even, rb, 0x7650u + j));
         v[2 * j + 1] = lds_f32<IMM>(prmt(odd, rb, 0x7650u + j));
       }
     } else {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
+      for (int k = 0; k < N; ++k) {
         const int sh = BITS * k - 2;
         const uint32_t off = sh >= 0 ? ((c32 >> (sh >= 0 ? sh : 0)) & (MASK << 2)) : ((c32 << (sh < 0 ? -sh : 0)) & (MASK << 2));
-        v[k] = lds_f32<IMM>(rb | off);
+        v[k] = lds_f32<IMM>((rb + lane_off) | off);
       }
     }
   } else {
-    const float4 a = lds_f32x4<IMM>(rb);
-    const float4 b = lds_f32x4<IMM + 16>(rb);
+    const float4 a = lds_f32x4<IMM>(rb + lane_off);
+    const float4 b = lds_f32x4<IMM + 16>(rb + lane_off);
     const int zc = __float_as_int(b.y);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
+    for (int k = 0; k < N; ++k) {
       const int c = (int)((codes >> (BITS * k)) & MASK);
       const int n = c - zc;
       const float e = n >= 0 ? ex2f((float)n * a.w) : ex2f((float)(-n) * b.x);
