@@ -38,6 +38,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 LAYERS, BATCH, KVH, QH, CTX, RES, D, GROUP = 36, 64, 8, 32, 4096, 128, 128, 64
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_tiles_kernel launch at 4 bits, per sequence, from the
+# ncu capture summarised in profiles/decode_tiles_4bit_b32.md (batch 32: 168.26 MB + 4.00 MB); traffic is
+# proportional to the batch, so a batch-64 launch is twice the captured one.
+NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_257_024 + 4_001_024) / 32
 
 
 def algorithmic_bytes(bits: int, batch=BATCH, sq=CTX, res=RES, meta=2, elem=2) -> int:
@@ -249,10 +253,10 @@ def run_ours(args) -> dict:
                    "parallelism": f"batch-sharded x{world}, no collective",
                    "l2_policy": f"inputs larger than L2: {L} distinct layer caches walked per step"},
         "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "decode_tiles_kernel + combine_tiles_kernel",
+                     "traffic": NCU_DRAM_BYTES_PER_SEQ_4BIT * B if bits == 4 else None, "peak_kind": peak_kind, "kernel": "decode_tiles_kernel + combine_tiles_kernel",
                      "bytes_per_launch": abytes, "us_per_launch": attn_us},
         "clocks": clocks,
     }

@@ -447,37 +447,62 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
   write_partial();
 }
 
-// ---- merge of the records of one (batch, kv head) pair
-__global__ void __launch_bounds__(128) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
-  const int pair = blockIdx.x, d = threadIdx.x;
+// ---- merge of the records of one (batch, kv head) pair: one CTA per pair, one warp-quad (128
+// threads) per query head.  Thread 0 lists the record slots of the warps whose tile ranges meet
+// this pair (from the same partition formula the main kernel uses); everyone then merges them.
+constexpr int kMaxCombineSlots = 64;
+__global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
+  __shared__ long long s_slot[kMaxCombineSlots];
+  __shared__ int s_n;
+  __shared__ long long s_first;
+  const int pair = blockIdx.x;
   const long long N = p.tp.total_tiles;
   const int W = p.tp.total_warps, T = p.tp.tiles_per_pair, gqa = p.gqa;
   const long long lo = (long long)pair * T, hi = lo + T;
-  long long g = lo * W / N;
-  if (g >= W) g = W - 1;
-  while (g + 1 < W && (g + 1) * N / W <= lo) ++g;
-  while (g > 0 && g * N / W > lo) --g;
-  const int g_first = (int)g;
-  for (int h = 0; h < gqa; ++h) {
-    float mx = -INFINITY;
-    for (int gw = g_first; gw < W; ++gw) {
-      const long long f0 = (long long)gw * N / W, f1 = (long long)(gw + 1) * N / W;
+  if (threadIdx.x == 0) {
+    long long g = lo * W / N;
+    if (g >= W) g = W - 1;
+    while (g + 1 < W && (g + 1) * N / W <= lo) ++g;
+    while (g > 0 && g * N / W > lo) --g;
+    s_first = g;
+    int n = 0;
+    for (long long gw = g; gw < W; ++gw) {
+      const long long f0 = gw * N / W, f1 = (gw + 1) * N / W;
       if (f0 >= hi) break;
       if (f1 <= lo || f0 >= f1) continue;
-      const long long slot = ((long long)gw * p.tp.max_segs + (pair - (int)(f0 / T))) * gqa + h;
-      mx = fmaxf(mx, p.part.m[slot]);
+      if (n < kMaxCombineSlots) s_slot[n] = gw * p.tp.max_segs + (pair - (int)(f0 / T));
+      ++n;
     }
+    s_n = n;
+  }
+  __syncthreads();
+  const int n = s_n;
+  const bool listed = n <= kMaxCombineSlots;
+  // record slot of the i-th contributing warp (listed), or a walk over the warps (more than 64 splits)
+  auto for_each_slot = [&](auto&& fn) {
+    if (listed) {
+      for (int i = 0; i < n; ++i) fn(s_slot[i]);
+    } else {
+      for (long long gw = s_first; gw < W; ++gw) {
+        const long long f0 = gw * N / W, f1 = (gw + 1) * N / W;
+        if (f0 >= hi) break;
+        if (f1 <= lo || f0 >= f1) continue;
+        fn(gw * p.tp.max_segs + (pair - (int)(f0 / T)));
+      }
+    }
+  };
+  for (int h = threadIdx.x >> 7; h < gqa; h += blockDim.x >> 7) {
+    const int d = threadIdx.x & 127;
+    float mx = -INFINITY;
+    for_each_slot([&](long long sl) { mx = fmaxf(mx, p.part.m[sl * gqa + h]); });
     float lsum = 0.f, a = 0.f;
-    for (int gw = g_first; gw < W; ++gw) {
-      const long long f0 = (long long)gw * N / W, f1 = (long long)(gw + 1) * N / W;
-      if (f0 >= hi) break;
-      if (f1 <= lo || f0 >= f1) continue;
-      const long long slot = ((long long)gw * p.tp.max_segs + (pair - (int)(f0 / T))) * gqa + h;
+    for_each_slot([&](long long sl) {
+      const long long slot = sl * gqa + h;
       const float mi = p.part.m[slot];
       const float wgt = mi > -INFINITY ? __expf(mi - mx) : 0.f;
       lsum = fmaf(p.part.l[slot], wgt, lsum);
       a = fmaf(p.part.acc[slot * D + d], wgt, a);
-    }
+    });
     const long long row = (long long)pair * gqa + h;
     if (o.out) mz_store_from_float(o.out, row * D + d, a / fmaxf(lsum, 1e-20f), o.out_dt);
     else {
@@ -626,7 +651,8 @@ int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st) {
 }
 
 int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t st) {
-  mzt::combine_tiles_kernel<<<(unsigned)(p.s.batch * p.s.kv_heads), 128, 0, st>>>(p, o);
+  if (p.tp.max_segs < 1) return mz_fail(MZ_ERR_ARG, "bad plan");
+  mzt::combine_tiles_kernel<<<(unsigned)(p.s.batch * p.s.kv_heads), 128 * (p.gqa < 4 ? p.gqa : 4), 0, st>>>(p, o);
   MZ_LAUNCH_CHECK("combine_tiles");
   return MZ_OK;
 }
