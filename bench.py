@@ -298,6 +298,58 @@ def run_attention_only(args) -> dict:
             "bytes_per_call": abytes, "achieved_gbs": abytes / us / 1e3, "frac_of_peak": abytes / us / 1e3 / peak, "peak_kind": kind}
 
 
+def run_generate(args) -> dict:
+    """BASELINE config 2 (secondary workload): greedy `generate()` on a random-init (std 0.02)
+    Qwen3-8B-architecture decoder in bf16 through `patch_transformers()` and
+    `cache_implementation="mu_zero_{bits}bit"`; decode-only tokens/s (prefill excluded, as the
+    reference's throughput bench does).  `--cache dynamic` runs stock transformers for context."""
+    import muzero
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    from transformers.generation.streamers import BaseStreamer
+    muzero.patch_transformers()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    cfg = Qwen3Config(num_hidden_layers=args.layers, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                      head_dim=128, intermediate_size=12288, vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1e6,
+                      max_position_embeddings=40960, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = Qwen3ForCausalLM(cfg).to(torch.bfloat16).eval()
+        for prm in model.parameters():
+            if prm.dim() > 1:
+                prm.data.normal_(0.0, 0.02)
+    gen = torch.Generator(device=device).manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (args.batch, args.context), device=device, generator=gen)
+
+    class Clock(BaseStreamer):
+        """Records the wall-clock time (after a device sync) at which each new token arrives."""
+        def __init__(self):
+            self.stamps = []
+        def put(self, value):
+            torch.cuda.synchronize()
+            self.stamps.append(time.perf_counter())
+        def end(self):
+            pass
+
+    kwargs = dict(max_new_tokens=args.new_tokens, do_sample=False, pad_token_id=0)
+    if args.cache == "mu_zero":
+        kwargs.update(cache_implementation=f"mu_zero_{args.bits}bit",
+                      cache_config={"q_group_size": GROUP, "residual_length": RES, "backend": "cuda"})
+    clock = Clock()
+    muzero.reset_mu_zero_decode_stats()
+    torch.cuda.reset_peak_memory_stats()
+    with torch.no_grad():
+        out = model.generate(input_ids=ids, attention_mask=torch.ones_like(ids), streamer=clock, **kwargs)
+    # stamps[0] = prompt echo, stamps[1] = first new token (end of prefill); decode = the rest
+    t = clock.stamps
+    decode_s = t[-1] - t[1]
+    steps = len(t) - 2
+    return {"mode": "generate", "cache": args.cache, "bits": args.bits, "layers": args.layers, "batch": args.batch,
+            "context": args.context, "new_tokens": int(out.shape[1] - ids.shape[1]),
+            "prefill_s": t[1] - t[0], "decode_tokens_per_s": args.batch * steps / decode_s, "ms_per_decode_step": 1e3 * decode_s / steps,
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30, "decode_stats": muzero.get_mu_zero_decode_stats()}
+
+
 def cpu_baseline(bits: int, seconds: float) -> dict:
     """The oracle (CPU restatement of the reference's torch path) on a bounded sample of the workload."""
     import importlib.util
@@ -359,8 +411,15 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--attention-only", action="store_true", help="small profiling case: only the fused attention calls")
+    ap.add_argument("--generate", action="store_true", help="secondary workload: HF generate() on a Qwen3-8B shaped model")
+    ap.add_argument("--cache", default="mu_zero", choices=["mu_zero", "dynamic"])
+    ap.add_argument("--context", type=int, default=CTX)
+    ap.add_argument("--new-tokens", type=int, default=128)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.generate:
+        print(json.dumps(run_generate(args)))
+        return
     if args.attention_only:
         print(json.dumps(run_attention_only(args)))
         return
