@@ -56,18 +56,14 @@ struct MzQuantRow {
     float unit = TT::round(__fdiv_rn(TT::round(__fsub_rn(x, lo)), span));
     if (unit != unit || anchor != anchor) return 0;
     unit = fminf(fmaxf(unit, 0.0f), 1.0f);
-    float q;
-    if (unit >= anchor) {
-      float p = TT::round(__fdiv_rn(TT::round(__fsub_rn(unit, anchor)), room_up));
-      if (p != p) return 0;
-      p = fminf(fmaxf(p, 0.0f), 1.0f);
-      q = TT::round(__fadd_rn(zero_code, rintf(TT::round(__fmul_rn(compand(p), steps_up)))));
-    } else {
-      float p = TT::round(__fdiv_rn(TT::round(__fsub_rn(anchor, unit)), room_dn));
-      if (p != p) return 0;
-      p = fminf(fmaxf(p, 0.0f), 1.0f);
-      q = TT::round(__fsub_rn(zero_code, rintf(TT::round(__fmul_rn(compand(p), steps_dn)))));
-    }
+    // one path for both sides of the zero anchor (lanes of a warp straddle it): round(a-b) == -round(b-a)
+    const bool up = unit >= anchor;
+    const float num = fabsf(TT::round(__fsub_rn(unit, anchor)));
+    float p = TT::round(__fdiv_rn(num, up ? room_up : room_dn));
+    if (p != p) return 0;
+    p = fminf(fmaxf(p, 0.0f), 1.0f);
+    const float rr = rintf(TT::round(__fmul_rn(compand(p), up ? steps_up : steps_dn)));
+    float q = TT::round(up ? __fadd_rn(zero_code, rr) : __fsub_rn(zero_code, rr));
     q = fminf(fmaxf(q, 0.0f), top);
     return (int)q;
   }
