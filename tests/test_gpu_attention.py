@@ -172,3 +172,53 @@ def test_hook_contract_and_stats(oracle):
     st = mz.get_mu_zero_decode_stats()
     assert st["calls"] == 1 and st["returns"] == 1 and st["fused_qk_success"] == 1 and st["fused_av_success"] == 1
     assert st["non_decode_query"] == 1 and st["missing_layer"] == 1
+
+
+@pytest.mark.parametrize("dtype", [torch.float16])
+def test_fp16_cache(oracle, dtype):
+    """K/V, query and residual in fp16 (the reference's unit tests use fp16 caches)."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
+    k, v, q = oracle.synth_kv(2, 2, 450, 128, 8, seed=55, dtype=dtype)
+    ref = oracle.OracleCacheLayer(bits=4, group=64, residual=128)
+    ref.append(k, v)
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig())
+    layer.update(k.cuda(), v.cuda(), {"materialize_full_kv": False})
+    assert torch.equal(layer._packed_key_q.cpu(), ref.packed_k) and torch.equal(layer._packed_value_q.cpu(), ref.packed_v)
+    want = oracle.decode_attention_oracle(q, ref, 128 ** -0.5, 4, compute_dtype=torch.float32)
+    got = decode_attention(layer, q.cuda(), 128 ** -0.5, out_dtype=torch.float32)
+    assert (got.cpu() - want).abs().max().item() <= TOL
+    assert decode_attention(layer, q.cuda(), 128 ** -0.5).dtype == torch.float16
+
+
+def test_edge_lengths(oracle):
+    """One residual token only; residual_length 0 with everything flushed; ragged residual tile."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
+    for S, R, steps in ((1, 128, 0), (64, 0, 0), (64, 0, 1), (129, 128, 0), (191, 64, 2)):
+        k, v, q = oracle.synth_kv(1, 2, S + steps, 128, 8, seed=S + R)
+        ref = oracle.OracleCacheLayer(bits=4, group=64, residual=R)
+        layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(residual_length=R))
+        ref.append(k[:, :, :S].contiguous(), v[:, :, :S].contiguous())
+        layer.update(k[:, :, :S].cuda().contiguous(), v[:, :, :S].cuda().contiguous(), {"materialize_full_kv": False})
+        for i in range(S, S + steps):
+            ref.append(k[:, :, i:i + 1].contiguous(), v[:, :, i:i + 1].contiguous())
+            layer.update(k[:, :, i:i + 1].cuda(), v[:, :, i:i + 1].cuda(), {"materialize_full_kv": False})
+        want = oracle.decode_attention_oracle(q, ref, 0.09, 4, compute_dtype=torch.float32)
+        got = decode_attention(layer, q.cuda(), 0.09, out_dtype=torch.float32)
+        assert (got.cpu() - want).abs().max().item() <= TOL, (S, R, steps)
+
+
+def test_long_context_many_warps(oracle):
+    """32k tokens of one sequence: every warp of the grid gets a slice of the same (b, kv head) pair."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
+    k, v, q = oracle.synth_kv(1, 1, 32768 + 100, 128, 4, seed=99)
+    ref = oracle.OracleCacheLayer(bits=2, group=64, residual=128, alpha_key=2.0, alpha_value=2.0)
+    ref.append(k, v)
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=2, alpha_key=2.0, alpha_value=2.0))
+    layer.update(k.cuda(), v.cuda(), {"materialize_full_kv": False})
+    assert torch.equal(layer._packed_key_q.cpu(), ref.packed_k)
+    want = oracle.decode_attention_oracle(q, ref, 128 ** -0.5, 4, compute_dtype=torch.float32)
+    got = decode_attention(layer, q.cuda(), 128 ** -0.5, out_dtype=torch.float32)
+    assert (got.cpu() - want).abs().max().item() <= TOL
