@@ -17,10 +17,27 @@ struct MzPartials {
 // is cut into `total_warps` contiguous ranges, one per warp.
 struct MzTilesPlan {
   int total_warps, warps_per_cta, ctas, max_segs;
-  int tiles_per_pair;      // k_groups + ceil(res_len / G)
+  int tiles_per_pair;      // k_groups packed tiles + ceil(res_len / dense_tokens) residual tiles
   long long total_tiles;   // pairs * tiles_per_pair
   unsigned smem_bytes, smem_per_warp;
+  // Work is cut into per-warp ranges by cost, not by tile count: a packed tile of G tokens costs
+  // cost_q, a residual tile of dense_tokens un-quantized tokens costs cost_d.
+  int packed_tiles, dense_tokens, cost_q, cost_d;
+  long long pair_cost, total_cost;   // packed_tiles*cost_q + dense_tiles*cost_d ; pairs * pair_cost
 };
+
+// Number of tiles (in flat order: pair-major, packed tiles before residual tiles) whose start cost
+// is below `c`.  Warp g owns the tiles [mz_tiles_before(g*total_cost/W), mz_tiles_before((g+1)*total_cost/W)).
+__host__ __device__ inline long long mz_tiles_before(const MzTilesPlan& t, long long c) {
+  const long long pair = c / t.pair_cost, r = c % t.pair_cost;
+  const long long qcost = (long long)t.packed_tiles * t.cost_q;
+  const long long in = r <= qcost ? (r + t.cost_q - 1) / t.cost_q : t.packed_tiles + (r - qcost + t.cost_d - 1) / t.cost_d;
+  return pair * t.tiles_per_pair + in;
+}
+__host__ __device__ inline void mz_warp_tiles(const MzTilesPlan& t, long long g, long long* f0, long long* f1) {
+  *f0 = mz_tiles_before(t, g * t.total_cost / t.total_warps);
+  *f1 = mz_tiles_before(t, (g + 1) * t.total_cost / t.total_warps);
+}
 
 struct MzDecodeParams {
   mz_kv_store s;

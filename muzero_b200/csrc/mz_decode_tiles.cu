@@ -21,15 +21,17 @@ struct Warp {
   using C = Cfg<BITS, G, GQA>;
   float* books; uint8_t* kbuf; uint8_t* vbuf;
   float* pbuf; float* qbuf; float* corr;
-  const float2* univ_k; const float2* univ_v;
+  const float* univ_k; const float* univ_v;
   int lane, dl, q16;      // key phase: half-warp (row parity) and token slot within the row
 };
 
-// ---- per-row expansion data for one staged tile side (128 rows), row r at r * ROW_BYTES: rows
-// that one lookup instruction touches together (r, r+1) then sit in different bank halves.
-template <int BITS, int G, int GQA>
-__device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const uint8_t* meta, int meta_dt, const float2* univ,
-                                           float alpha, float lg2a) {
+// ---- per-row expansion data for one staged tile side (128 rows), one row per ROW_BYTES; the two
+// rows that one lookup instruction touches are neighbours, i.e. sit in different bank halves.
+// A pass covers D / PASSES rows: channels [pass*RP, +RP) of a key tile, tokens [pass*G/PASSES, ..) of
+// a value tile (all groups).
+template <int BITS, int G, int GQA, bool VALUES>
+__device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const uint8_t* meta, int meta_dt, const float* univ,
+                                           float alpha, float lg2a, int pass) {
   using C = Cfg<BITS, G, GQA>;
   constexpr int TOP = C::NE - 1;
   const uint8_t* lo_p = meta;
@@ -37,8 +39,12 @@ __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const ui
   // rotation of the 4-entry store groups that makes the 16-byte stores of 8 neighbouring lanes hit 8 bank groups
   const int rot = (w.lane >> 1) & 3;
 #pragma unroll
-  for (int i = 0; i < D / 32; ++i) {
-    const int r = w.lane + 32 * i;
+  for (int i = 0; i < C::RP / 32; ++i) {
+    // keys: slot = channel, natural order.  values: slot g*TP + t for token t of the pass and group g
+    // (metadata row t*NG + g), so that the rows of two consecutive tokens (the two half-warps of a
+    // lookup) are neighbours
+    const int slot = w.lane + 32 * i;
+    const int r = VALUES ? (pass * C::TP + slot % C::TP) * C::NG + slot / C::TP : pass * C::RP + slot;
     const float lo = meta_at(lo_p, r, meta_dt);
     const float span = meta_at(sp_p, r, meta_dt);
     // IEEE division and multiply: the zero code must round exactly as the dequantizer's does
@@ -49,33 +55,25 @@ __device__ __forceinline__ void build_rows(const Warp<BITS, G, GQA>& w, const ui
     const float A = fmaf(span, anchor, lo);
     const float Bup = span * fmaxf(1.0f - anchor, 1e-8f);
     const float Bdn = span * fmaxf(anchor, 1e-8f);
-    float* dst = w.books + r * C::BOOK_STRIDE;
+    float* dst = w.books + slot * C::BOOK_STRIDE;
     if (C::BOOKS) {
-      const float2* u = univ + zc * (C::NE + 1);
-      if (C::NE >= 16) {
+      // entry e = A + B * shape[zc][e], B = Bup at and above the zero code (shape >= 0), Bdn below it
+      const float* u = univ + zc * C::UROW;
+      if (C::NE >= 4) {
 #pragma unroll
         for (int g = 0; g < C::NE / 4; ++g) {
-          const int e = ((g + rot) & (C::NE / 4 - 1)) * 4;
+          const int e = (C::NE >= 16 ? ((g + rot) & (C::NE / 4 - 1)) : g) * 4;
+          const float4 u4 = *(const float4*)(u + e);
           float4 o4;
-          o4.x = fmaf(Bdn, u[e].y, fmaf(Bup, u[e].x, A));
-          o4.y = fmaf(Bdn, u[e + 1].y, fmaf(Bup, u[e + 1].x, A));
-          o4.z = fmaf(Bdn, u[e + 2].y, fmaf(Bup, u[e + 2].x, A));
-          o4.w = fmaf(Bdn, u[e + 3].y, fmaf(Bup, u[e + 3].x, A));
-          *(float4*)(dst + e) = o4;
-        }
-      } else if (C::NE >= 4) {
-#pragma unroll
-        for (int e = 0; e < C::NE; e += 4) {
-          float4 o4;
-          o4.x = fmaf(Bdn, u[e].y, fmaf(Bup, u[e].x, A));
-          o4.y = fmaf(Bdn, u[e + 1].y, fmaf(Bup, u[e + 1].x, A));
-          o4.z = fmaf(Bdn, u[e + 2].y, fmaf(Bup, u[e + 2].x, A));
-          o4.w = fmaf(Bdn, u[e + 3].y, fmaf(Bup, u[e + 3].x, A));
+          o4.x = fmaf(u4.x < 0.f ? Bdn : Bup, u4.x, A);
+          o4.y = fmaf(u4.y < 0.f ? Bdn : Bup, u4.y, A);
+          o4.z = fmaf(u4.z < 0.f ? Bdn : Bup, u4.z, A);
+          o4.w = fmaf(u4.w < 0.f ? Bdn : Bup, u4.w, A);
           *(float4*)(dst + e) = o4;
         }
       } else {
-        dst[0] = fmaf(Bdn, u[0].y, fmaf(Bup, u[0].x, A));
-        dst[1] = fmaf(Bdn, u[1].y, fmaf(Bup, u[1].x, A));
+        dst[0] = fmaf(u[0] < 0.f ? Bdn : Bup, u[0], A);
+        dst[1] = fmaf(u[1] < 0.f ? Bdn : Bup, u[1], A);
       }
     } else {
       const float inv_a = 1.0f / alpha;
@@ -123,16 +121,16 @@ __device__ __forceinline__ void softmax_tile(const Warp<BITS, G, GQA>& w, float 
 }
 
 template <int BITS, int G, int GQA>
-__global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodeParams p) {
+__global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_tiles_kernel(const MzDecodeParams p) {
   using C = Cfg<BITS, G, GQA>;
   extern __shared__ __align__(16) uint8_t smem[];
   const mz_kv_store& s = p.s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // universal signed shape tables: row zc, entry e -> (up part, down part) of the normalised value
+  // signed shape tables: row zc, entry e -> normalised value of code e (>= 0 at and above the zero code, < 0 below)
   uint8_t* smem_al = smem + ((256u - ((unsigned)__cvta_generic_to_shared(smem) & 255u)) & 255u);
-  float2* univ_k = (float2*)smem_al;
-  float2* univ_v = univ_k + C::UNIV_FLOAT2;
+  float* univ_k = (float*)smem_al;
+  float* univ_v = univ_k + C::UNIV_FLOATS;
   if (C::BOOKS) {
     constexpr int TOP = C::NE - 1;
     for (int i = threadIdx.x; i < 2 * C::NE * C::NE; i += blockDim.x) {
@@ -140,24 +138,24 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
       const int zc = j / C::NE, e = j % C::NE;
       const float alpha = which ? s.alpha_value : s.alpha_key;
       const float lb = log1pf(alpha);
-      float2 u = make_float2(0.f, 0.f);
+      float u;
       if (e >= zc) {
         const int up = max(TOP - zc, 1);
-        u.x = expm1f((float)min(e - zc, up) / (float)up * lb) / alpha;
+        u = expm1f((float)min(e - zc, up) / (float)up * lb) / alpha;
       } else {
         const int dn = max(zc, 1);
-        u.y = -expm1f((float)(zc - e) / (float)dn * lb) / alpha;
+        u = -expm1f((float)(zc - e) / (float)dn * lb) / alpha;
       }
-      (which ? univ_v : univ_k)[zc * (C::NE + 1) + e] = u;
+      (which ? univ_v : univ_k)[zc * C::UROW + e] = u;
     }
   }
   __syncthreads();
 
-  const long long N = p.tp.total_tiles;
   const int W = p.tp.total_warps, T = p.tp.tiles_per_pair;
   const int gw = blockIdx.x * (blockDim.x >> 5) + warp;
   if (gw >= W) return;
-  const long long f0 = (long long)gw * N / W, f1 = (long long)(gw + 1) * N / W;
+  long long f0, f1;
+  mz_warp_tiles(p.tp, gw, &f0, &f1);
   if (f0 >= f1) return;
 
   Warp<BITS, G, GQA> w;
@@ -176,42 +174,61 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
   const int nq = s.k_groups * G;
   const uint32_t books_sa = (uint32_t)__cvta_generic_to_shared(w.books);
 
-  auto stage_k = [&](long long f) {
-    if (f < f1) {
-      const int pair = (int)(f / T), tile = (int)(f % T);
+  // position of a tile; walked incrementally (no divisions in the tile loop)
+  struct Cursor { int pair, tile, b, kvh; };
+  auto advance = [&](Cursor& c) {
+    if (++c.tile == T) {
+      c.tile = 0; ++c.pair;
+      if (++c.kvh == s.kv_heads) { c.kvh = 0; ++c.b; }
+    }
+  };
+  // residual tile: up to DT rows of 128 un-quantized elements, 16 lanes per row
+  auto stage_dense = [&](uint8_t* dst, const uint16_t* res, int b, int kvh, int tile) {
+    const int tok0 = (tile - s.k_groups) * C::DT;
+    const int ntok = min(C::DT, s.res_len - tok0);
+    const uint16_t* src = res + b * s.res_stride_b + kvh * s.res_stride_h + (long long)(s.res_start + tok0) * s.res_stride_t;
+    for (int i = lane; i < ntok * 16; i += 32) cp_async16(dst + i * 16, src + (long long)(i >> 4) * s.res_stride_t + (i & 15) * 8);
+  };
+  auto stage_k = [&](const Cursor& c, bool valid) {
+    if (valid) {
+      const int b = c.b, kvh = c.kvh, tile = c.tile;
       if (tile < s.k_groups) {
-        const int b = pair / s.kv_heads, kvh = pair % s.kv_heads;
         const uint8_t* src = s.packed_k + b * s.pk_stride_b + kvh * s.pk_stride_h + (long long)tile * C::TILE_BYTES;
         warp_copy_async(w.kbuf, src, C::TILE_BYTES, lane);
         const long long m0 = (b * s.km_stride_b + kvh * s.km_stride_h + (long long)tile * D) * msz;
-        warp_copy_async(w.kbuf + C::TILE_BYTES, (const uint8_t*)s.k_mn + m0, D * msz, lane);
-        warp_copy_async(w.kbuf + C::TILE_BYTES + C::META_BYTES / 2, (const uint8_t*)s.k_scale + m0, D * msz, lane);
+        warp_copy_async(w.kbuf + C::STAGE_BYTES, (const uint8_t*)s.k_mn + m0, D * msz, lane);
+        warp_copy_async(w.kbuf + C::STAGE_BYTES + C::META_BYTES / 2, (const uint8_t*)s.k_scale + m0, D * msz, lane);
+      } else {
+        stage_dense(w.kbuf, (const uint16_t*)s.res_k, b, kvh, tile);
       }
     }
     cp_async_commit();
   };
-  auto stage_v = [&](long long f) {
-    if (f < f1) {
-      const int pair = (int)(f / T), tile = (int)(f % T);
+  auto stage_v = [&](const Cursor& c, bool valid) {
+    if (valid) {
+      const int b = c.b, kvh = c.kvh, tile = c.tile;
       if (tile < s.k_groups) {
-        const int b = pair / s.kv_heads, kvh = pair % s.kv_heads;
         const uint8_t* src = s.packed_v + b * s.pv_stride_b + kvh * s.pv_stride_h + (long long)tile * C::TILE_BYTES;
         warp_copy_async(w.vbuf, src, C::TILE_BYTES, lane);
         const long long m0 = (b * s.vm_stride_b + kvh * s.vm_stride_h + (long long)tile * D) * msz;
-        warp_copy_async(w.vbuf + C::TILE_BYTES, (const uint8_t*)s.v_mn + m0, D * msz, lane);
-        warp_copy_async(w.vbuf + C::TILE_BYTES + C::META_BYTES / 2, (const uint8_t*)s.v_scale + m0, D * msz, lane);
+        warp_copy_async(w.vbuf + C::STAGE_BYTES, (const uint8_t*)s.v_mn + m0, D * msz, lane);
+        warp_copy_async(w.vbuf + C::STAGE_BYTES + C::META_BYTES / 2, (const uint8_t*)s.v_scale + m0, D * msz, lane);
+      } else {
+        stage_dense(w.vbuf, (const uint16_t*)s.res_v, b, kvh, tile);
       }
     }
     cp_async_commit();
   };
 
-  float2 out2[2][GQA];               // this lane's 4 channels (4*lane ..) as two pairs, per head
+  // value phase: lane (tp = lane>>4, j = lane&15) owns, in every group g, channels g*G + j*TPL .. +TPL-1
+  // (8 channels in all) of the tokens of parity tp; pairs of neighbouring channels per head
+  float2 out2[4][GQA];
   float m_st[C::ROUNDS], l_st[C::ROUNDS];
   int cur_pair = -1, seg = 0;
 
   auto reset_state = [&]() {
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int h = 0; h < GQA; ++h) out2[j][h] = make_float2(0.f, 0.f);
 #pragma unroll
@@ -220,8 +237,21 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
   auto write_partial = [&]() {
     const long long slot0 = ((long long)gw * p.tp.max_segs + seg) * GQA;
 #pragma unroll
-    for (int h = 0; h < GQA; ++h)
-      *(float4*)(p.part.acc + (slot0 + h) * D + lane * 4) = make_float4(out2[0][h].x, out2[0][h].y, out2[1][h].x, out2[1][h].y);
+    for (int h = 0; h < GQA; ++h) {
+      float2 t[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {      // add the tokens of the other parity
+        t[j].x = out2[j][h].x + __shfl_xor_sync(0xffffffffu, out2[j][h].x, 16);
+        t[j].y = out2[j][h].y + __shfl_xor_sync(0xffffffffu, out2[j][h].y, 16);
+      }
+      if (lane < 16) {
+        float* dst = p.part.acc + (slot0 + h) * D;
+#pragma unroll
+        for (int g = 0; g < C::NG; ++g)
+#pragma unroll
+          for (int k = 0; k < C::TPL; k += 2) *(float2*)(dst + g * G + lane * C::TPL + k) = t[g * (C::TPL / 2) + k / 2];
+      }
+    }
 #pragma unroll
     for (int r = 0; r < C::ROUNDS; ++r) {
       const int h = 2 * r + w.dl;
@@ -232,11 +262,15 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
     }
   };
 
-  stage_k(f0);
-  stage_v(f0);
-  for (long long f = f0; f < f1; ++f) {
-    const int pair = (int)(f / T), tile = (int)(f % T);
-    const int b = pair / s.kv_heads, kvh = pair % s.kv_heads;
+  Cursor cur;
+  cur.pair = (int)(f0 / T); cur.tile = (int)(f0 % T);
+  cur.b = cur.pair / s.kv_heads; cur.kvh = cur.pair % s.kv_heads;
+  Cursor nxt = cur;
+  stage_k(cur, true);
+  stage_v(cur, true);
+  for (int left = (int)(f1 - f0); left > 0; --left, cur = nxt) {
+    const int pair = cur.pair, tile = cur.tile, b = cur.b, kvh = cur.kvh;
+    advance(nxt);
     if (pair != cur_pair) {
       if (cur_pair >= 0) { write_partial(); ++seg; }
       cur_pair = pair;
@@ -250,8 +284,8 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
       __syncwarp();
     }
     const bool dense = tile >= s.k_groups;
-    const int tok0 = dense ? (tile - s.k_groups) * G : tile * G;      // first token inside its region
-    const int ntok = dense ? min(G, s.res_len - tok0) : G;
+    const int tok0 = dense ? (tile - s.k_groups) * C::DT : tile * G;      // first token inside its region
+    const int ntok = dense ? min(C::DT, s.res_len - tok0) : G;
     const long long mask0 = p.mask ? b * p.mask_stride_b + (dense ? nq : 0) + tok0 : 0;
     float sl[C::ROUNDS][C::TPL];
 
@@ -259,20 +293,23 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
     __syncwarp();
     if (!dense) {
       // ---------------- keys: expansion rows, then QK with all heads per code
-      build_rows<BITS, G, GQA>(w, w.kbuf + C::TILE_BYTES, s.meta_dtype, w.univ_k, s.alpha_key, lg2a_k);
-      __syncwarp();
       float2 acc2[C::TPL / 2][GQA];      // token pairs (2j, 2j+1)
 #pragma unroll
       for (int k = 0; k < C::TPL / 2; ++k)
 #pragma unroll
         for (int h = 0; h < GQA; ++h) acc2[k][h] = make_float2(0.f, 0.f);
-      {
+#pragma unroll 1
+      for (int pass = 0; pass < C::PASSES; ++pass) {
+        if (pass) __syncwarp();                               // every lane is done with the previous pass' rows
+        build_rows<BITS, G, GQA, false>(w, w.kbuf + C::STAGE_BYTES, s.meta_dtype, w.univ_k, s.alpha_key, lg2a_k, pass);
+        __syncwarp();
         const uint32_t lane_off = w.dl * C::ROW_BYTES;        // row 2*step + dl
         const uint8_t* krow = w.kbuf + w.dl * C::QB;
         const float* qd = w.qbuf + w.dl * GQA;
+        const int sb0 = pass * (C::KSTEPS / C::PASSES);
 #pragma unroll 1
-        for (int sb = 0; sb < C::KSTEPS; sb += C::UNROLL) {
-          const uint32_t rb = books_sa + sb * (2 * C::ROW_BYTES);
+        for (int sb = sb0; sb < sb0 + C::KSTEPS / C::PASSES; sb += C::UNROLL) {
+          const uint32_t rb = books_sa + (sb - sb0) * (2 * C::ROW_BYTES);
           auto one_step = [&](auto uc) {
             constexpr int u = decltype(uc)::value;
             const int step = sb + u;
@@ -322,35 +359,59 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
           sl[r][k] = val;
         }
     } else {
-      // ---------------- dense residual keys: one token per lane, logits exchanged through shared memory
+      // ---------------- residual keys (staged rows of 128 elements): half-warp dl takes tokens
+      // NB*(2*batch + dl) .. +NB-1, lane j of it channels 8j .. 8j+7; the 16 partial dots of every
+      // (token, head) are then summed by a reduce-scatter; logits go through shared memory
       float* sbuf = w.pbuf;
-      const uint16_t* rk = (const uint16_t*)s.res_k + b * s.res_stride_b + kvh * s.res_stride_h;
+      for (int i = lane; i < G * GQA; i += 32) sbuf[i] = -INFINITY;
+      constexpr int HB = GQA > 4 ? 4 : GQA;             // heads per sweep (bounds the registers held)
+      constexpr int NB = 32 / HB;                       // tokens per half-warp and batch: 32 partial sums per lane
+      __syncwarp();
 #pragma unroll 1
-      for (int i = 0; i < G / 32; ++i) {
-        const int t = lane + 32 * i;
-        float dot[GQA];
+      for (int h0 = 0; h0 < GQA; h0 += HB) {
+        float qr[8][HB];
 #pragma unroll
-        for (int h = 0; h < GQA; ++h) dot[h] = 0.f;
-        if (t < ntok) {
-          const uint4* row = (const uint4*)(rk + (long long)(s.res_start + tok0 + t) * s.res_stride_t);
-#pragma unroll 4
-          for (int c = 0; c < D / 8; ++c) {
-            const uint4 raw = __ldg(row + c);
+        for (int c = 0; c < 8; ++c)
+#pragma unroll
+          for (int h = 0; h < HB; ++h) qr[c][h] = w.qbuf[(w.q16 * 8 + c) * GQA + h0 + h];
+#pragma unroll 1
+        for (int t0 = 0; t0 < ntok; t0 += 2 * NB) {
+          float part[32];
+#pragma unroll
+          for (int tt = 0; tt < NB; ++tt) {
+            const int t = min(t0 + w.dl * NB + tt, C::DT - 1);   // rows past ntok hold stale bytes; their logits are dropped below
+            const uint4 raw = *(const uint4*)(w.kbuf + t * (2 * D) + w.q16 * 16);
             const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+            float dot[HB];
+#pragma unroll
+            for (int h = 0; h < HB; ++h) dot[h] = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 x = unpack2(ww[e], s.kv_dtype);
-              const int d = c * 8 + 2 * e;
 #pragma unroll
-              for (int h = 0; h < GQA; ++h) {
-                dot[h] = fmaf(x.x, w.qbuf[d * GQA + h], dot[h]);
-                dot[h] = fmaf(x.y, w.qbuf[(d + 1) * GQA + h], dot[h]);
-              }
+              for (int h = 0; h < HB; ++h) dot[h] = fmaf(x.y, qr[2 * e + 1][h], fmaf(x.x, qr[2 * e][h], dot[h]));
+            }
+#pragma unroll
+            for (int h = 0; h < HB; ++h) part[tt * HB + h] = dot[h];
+          }
+          // reduce-scatter over the 16 lanes of the half-warp: lane j ends with sums 2j and 2j+1
+#pragma unroll
+          for (int n = 16, bit = 8; bit >= 1; n >>= 1, bit >>= 1) {
+            const bool upper = (w.q16 & bit) != 0;
+#pragma unroll
+            for (int i = 0; i < n; ++i) {
+              const float keep = upper ? part[i + n] : part[i];
+              const float send = upper ? part[i] : part[i + n];
+              part[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
             }
           }
-        }
 #pragma unroll
-        for (int h = 0; h < GQA; ++h) sbuf[t * GQA + h] = t < ntok ? dot[h] : -INFINITY;
+          for (int i = 0; i < 2; ++i) {
+            const int idx = 2 * w.q16 + i;
+            const int t = t0 + w.dl * NB + idx / HB;
+            if (t < ntok) sbuf[t * GQA + h0 + idx % HB] = part[i];
+          }
+        }
       }
       __syncwarp();
 #pragma unroll
@@ -361,7 +422,7 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
       }
     }
     __syncwarp();                 // every lane is done with kbuf, the rows and sbuf
-    stage_k(f + 1);
+    stage_k(nxt, left > 1);
     if (p.mask) {
 #pragma unroll
       for (int k = 0; k < C::TPL; ++k) {
@@ -381,42 +442,49 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
       for (int h = 0; h < GQA; ++h) { cr[h] = w.corr[h]; rescale |= cr[h] != 1.0f; }
       if (rescale) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
           for (int h = 0; h < GQA; ++h) { out2[j][h].x *= cr[h]; out2[j][h].y *= cr[h]; }
       }
     }
     if (!dense) {
-      build_rows<BITS, G, GQA>(w, w.vbuf + C::TILE_BYTES, s.meta_dtype, w.univ_v, s.alpha_value, lg2a_v);
-      __syncwarp();
-      {
-        const int grp = (lane * 4) / G;
-        const uint32_t lane_off = grp * C::ROW_BYTES;         // row t*NG + grp
 #pragma unroll 1
-        for (int sb = 0; sb < C::VSTEPS; sb += C::UNROLL) {
-          const uint32_t rb = books_sa + sb * (C::NG * C::ROW_BYTES);
+      for (int pass = 0; pass < C::PASSES; ++pass) {
+        if (pass) __syncwarp();
+        build_rows<BITS, G, GQA, true>(w, w.vbuf + C::STAGE_BYTES, s.meta_dtype, w.univ_v, s.alpha_value, lg2a_v, pass);
+        __syncwarp();
+        const uint32_t lane_off = w.dl * C::ROW_BYTES;        // token 2*step + tp inside a step's pair of rows
+        const uint8_t* vrow = w.vbuf + w.dl * C::VROW_BYTES;
+        const float* pd = w.pbuf + w.dl * GQA;
+        const int sb0 = pass * (C::TP / 2);
+#pragma unroll 1
+        for (int sb = sb0; sb < sb0 + C::TP / 2; sb += C::UNROLL) {
+          const uint32_t rb = books_sa + (sb - sb0) * (2 * C::ROW_BYTES);
           auto one_step = [&](auto uc) {
             constexpr int u = decltype(uc)::value;
-            const int t = sb + u;
-            const unsigned long long codes = load_codes<BITS, 4>(w.vbuf + t * C::VROW_BYTES, lane * 4);
-            float v[4];
-            expand<BITS, C::BOOKS, C::PRMT_ADDR, 4, u * (C::NG * C::ROW_BYTES)>(codes, rb, lane_off, v);
+            const int step = sb + u;
             float ph[GQA];
             if (GQA % 4 == 0) {
 #pragma unroll
               for (int h = 0; h < GQA; h += 4) {
-                const float4 t4 = *(const float4*)(w.pbuf + t * GQA + h);
+                const float4 t4 = *(const float4*)(pd + step * (2 * GQA) + h);
                 ph[h] = t4.x; ph[h + 1] = t4.y; ph[h + 2] = t4.z; ph[h + 3] = t4.w;
               }
             } else {
 #pragma unroll
-              for (int h = 0; h < GQA; ++h) ph[h] = w.pbuf[t * GQA + h];
+              for (int h = 0; h < GQA; ++h) ph[h] = pd[step * (2 * GQA) + h];
             }
 #pragma unroll
-            for (int h = 0; h < GQA; ++h) {
-              const float2 pp = make_float2(ph[h], ph[h]);
-              ffma2(out2[0][h], make_float2(v[0], v[1]), pp);
-              ffma2(out2[1][h], make_float2(v[2], v[3]), pp);
+            for (int g = 0; g < C::NG; ++g) {
+              const unsigned long long codes = load_codes<BITS, C::TPL>(vrow + step * (2 * C::VROW_BYTES) + g * C::QB, w.q16 * C::TPL);
+              float v[C::TPL];
+              expand<BITS, C::BOOKS, C::PRMT_ADDR, C::TPL, u * (2 * C::ROW_BYTES)>(codes, rb + g * (C::TP * C::ROW_BYTES), lane_off, v);
+#pragma unroll
+              for (int h = 0; h < GQA; ++h) {
+                const float2 pp = make_float2(ph[h], ph[h]);
+#pragma unroll
+                for (int k = 0; k < C::TPL; k += 2) ffma2(out2[g * (C::TPL / 2) + k / 2][h], make_float2(v[k], v[k + 1]), pp);
+              }
             }
           };
           one_step(std::integral_constant<int, 0>{});
@@ -426,22 +494,25 @@ __global__ void __launch_bounds__(384, 1) decode_tiles_kernel(const MzDecodePara
         }
       }
     } else {
-      const uint16_t* rv = (const uint16_t*)s.res_v + b * s.res_stride_b + kvh * s.res_stride_h + lane * 4;
-#pragma unroll 4
-      for (int t = 0; t < ntok; ++t) {
-        const uint2 raw = __ldg((const uint2*)(rv + (long long)(s.res_start + tok0 + t) * s.res_stride_t));
-        const float2 x0 = unpack2(raw.x, s.kv_dtype), x1 = unpack2(raw.y, s.kv_dtype);
+      const uint16_t* rv = (const uint16_t*)w.vbuf + w.q16 * C::TPL;
+#pragma unroll 2
+      for (int t = w.dl; t < ntok; t += 2) {
+        const uint16_t* row = rv + t * D;
+        float ph[GQA];
 #pragma unroll
-        for (int h = 0; h < GQA; ++h) {
-          const float ph = w.pbuf[t * GQA + h];
-          const float2 pp = make_float2(ph, ph);
-          ffma2(out2[0][h], x0, pp);
-          ffma2(out2[1][h], x1, pp);
-        }
+        for (int h = 0; h < GQA; ++h) ph[h] = w.pbuf[t * GQA + h];
+#pragma unroll
+        for (int g = 0; g < C::NG; ++g)
+#pragma unroll
+          for (int k = 0; k < C::TPL; k += 2) {
+            const float2 x = unpack2(*(const uint32_t*)(row + g * G + k), s.kv_dtype);
+#pragma unroll
+            for (int h = 0; h < GQA; ++h) ffma2(out2[g * (C::TPL / 2) + k / 2][h], x, make_float2(ph[h], ph[h]));
+          }
       }
     }
     __syncwarp();                 // every lane is done with vbuf, the rows and pbuf
-    stage_v(f + 1);
+    stage_v(nxt, left > 1);
   }
   cp_async_wait<0>();
   write_partial();
@@ -456,18 +527,18 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
   __shared__ int s_n;
   __shared__ long long s_first;
   const int pair = blockIdx.x;
-  const long long N = p.tp.total_tiles;
   const int W = p.tp.total_warps, T = p.tp.tiles_per_pair, gqa = p.gqa;
   const long long lo = (long long)pair * T, hi = lo + T;
   if (threadIdx.x == 0) {
-    long long g = lo * W / N;
+    // first warp whose range reaches into this pair: start from the cost estimate, then settle
+    long long g = (long long)pair * p.tp.pair_cost * W / p.tp.total_cost, f0, f1;
     if (g >= W) g = W - 1;
-    while (g + 1 < W && (g + 1) * N / W <= lo) ++g;
-    while (g > 0 && g * N / W > lo) --g;
+    for (mz_warp_tiles(p.tp, g, &f0, &f1); g > 0 && f0 > lo; mz_warp_tiles(p.tp, g, &f0, &f1)) --g;
+    for (; g + 1 < W && f1 <= lo; mz_warp_tiles(p.tp, g, &f0, &f1)) ++g;
     s_first = g;
     int n = 0;
     for (long long gw = g; gw < W; ++gw) {
-      const long long f0 = gw * N / W, f1 = (gw + 1) * N / W;
+      mz_warp_tiles(p.tp, gw, &f0, &f1);
       if (f0 >= hi) break;
       if (f1 <= lo || f0 >= f1) continue;
       if (n < kMaxCombineSlots) s_slot[n] = gw * p.tp.max_segs + (pair - (int)(f0 / T));
@@ -484,7 +555,8 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
       for (int i = 0; i < n; ++i) fn(s_slot[i]);
     } else {
       for (long long gw = s_first; gw < W; ++gw) {
-        const long long f0 = gw * N / W, f1 = (gw + 1) * N / W;
+        long long f0, f1;
+        mz_warp_tiles(p.tp, gw, &f0, &f1);
         if (f0 >= hi) break;
         if (f1 <= lo || f0 >= f1) continue;
         fn(gw * p.tp.max_segs + (pair - (int)(f0 / T)));
@@ -543,33 +615,34 @@ int launch_group(const MzDecodeParams& p, cudaStream_t st) {
 }
 
 template <int BITS, int G, int GQA>
-void sizes_one(unsigned* per_warp, unsigned* shared) {
+void sizes_one(unsigned* per_warp, unsigned* shared, unsigned* stage) {
   *per_warp = Cfg<BITS, G, GQA>::PER_WARP;
   *shared = Cfg<BITS, G, GQA>::SHARED;
+  *stage = Cfg<BITS, G, GQA>::STAGE_BYTES;
 }
 template <int BITS, int G>
-void sizes_gqa(int gqa, unsigned* a, unsigned* b) {
-  if (gqa == 1) sizes_one<BITS, G, 1>(a, b);
-  else if (gqa == 2) sizes_one<BITS, G, 2>(a, b);
-  else if (gqa == 4) sizes_one<BITS, G, 4>(a, b);
-  else sizes_one<BITS, G, 8>(a, b);
+void sizes_gqa(int gqa, unsigned* a, unsigned* b, unsigned* c) {
+  if (gqa == 1) sizes_one<BITS, G, 1>(a, b, c);
+  else if (gqa == 2) sizes_one<BITS, G, 2>(a, b, c);
+  else if (gqa == 4) sizes_one<BITS, G, 4>(a, b, c);
+  else sizes_one<BITS, G, 8>(a, b, c);
 }
 template <int BITS>
-void sizes_group(int group, int gqa, unsigned* a, unsigned* b) {
-  if (group == 32) sizes_gqa<BITS, 32>(gqa, a, b);
-  else if (group == 64) sizes_gqa<BITS, 64>(gqa, a, b);
-  else sizes_gqa<BITS, 128>(gqa, a, b);
+void sizes_group(int group, int gqa, unsigned* a, unsigned* b, unsigned* c) {
+  if (group == 32) sizes_gqa<BITS, 32>(gqa, a, b, c);
+  else if (group == 64) sizes_gqa<BITS, 64>(gqa, a, b, c);
+  else sizes_gqa<BITS, 128>(gqa, a, b, c);
 }
-void sizes_any(int bits, int group, int gqa, unsigned* a, unsigned* b) {
+void sizes_any(int bits, int group, int gqa, unsigned* a, unsigned* b, unsigned* c) {
   switch (bits) {
-    case 1: sizes_group<1>(group, gqa, a, b); break;
-    case 2: sizes_group<2>(group, gqa, a, b); break;
-    case 3: sizes_group<3>(group, gqa, a, b); break;
-    case 4: sizes_group<4>(group, gqa, a, b); break;
-    case 5: sizes_group<5>(group, gqa, a, b); break;
-    case 6: sizes_group<6>(group, gqa, a, b); break;
-    case 7: sizes_group<7>(group, gqa, a, b); break;
-    default: sizes_group<8>(group, gqa, a, b); break;
+    case 1: sizes_group<1>(group, gqa, a, b, c); break;
+    case 2: sizes_group<2>(group, gqa, a, b, c); break;
+    case 3: sizes_group<3>(group, gqa, a, b, c); break;
+    case 4: sizes_group<4>(group, gqa, a, b, c); break;
+    case 5: sizes_group<5>(group, gqa, a, b, c); break;
+    case 6: sizes_group<6>(group, gqa, a, b, c); break;
+    case 7: sizes_group<7>(group, gqa, a, b, c); break;
+    default: sizes_group<8>(group, gqa, a, b, c); break;
   }
 }
 }  // namespace mzt
@@ -596,12 +669,13 @@ bool mz_decode_tiles_supported(const MzDecodeParams& p) {
 int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots) {
   const mz_kv_store& s = p.s;
   MzTilesPlan& t = p.tp;
-  unsigned per_warp = 0, shared = 0;
-  mzt::sizes_any(s.bits, s.group, p.gqa, &per_warp, &shared);
+  unsigned per_warp = 0, shared = 0, stage = 0;
+  mzt::sizes_any(s.bits, s.group, p.gqa, &per_warp, &shared, &stage);
   const unsigned budget = 220 * 1024;
   int warps = (int)((budget - shared) / per_warp);
   if (warps < 1) return mz_fail(MZ_ERR_UNSUPPORTED, "tile does not fit shared memory");
-  if (warps > 12) warps = 12;
+  const int max_warps = p.gqa > 4 ? 8 : 12;      // Cfg::MAX_WARPS
+  if (warps > max_warps) warps = max_warps;
   if (const char* e = std::getenv("MZ_TILES_WARPS")) {   // tuning aid: fewer warps per CTA
     const int w = atoi(e);
     if (w >= 1 && w < warps) warps = w;
@@ -609,23 +683,39 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
   t.warps_per_cta = warps;
   t.smem_per_warp = per_warp;
   t.smem_bytes = shared + per_warp * warps;
-  t.tiles_per_pair = s.k_groups + (s.res_len + s.group - 1) / s.group;
+  t.packed_tiles = s.k_groups;
+  t.dense_tokens = (int)(stage / (2 * mzt::D));
+  const int dense_tiles = (s.res_len + t.dense_tokens - 1) / t.dense_tokens;
+  t.tiles_per_pair = t.packed_tiles + dense_tiles;
+  // relative cost of a packed tile of `group` tokens and of a residual tile, fitted to per-warp times
+  // measured on B200 (4-bit and 2-bit caches, group 64)
+  t.cost_q = s.group + 10;
+  t.cost_d = t.dense_tokens + 16;
+  if (const char* e = std::getenv("MZ_TILES_DENSE_COST")) {   // tuning aid
+    const int c = atoi(e);
+    if (c >= 1 && c <= 4096) t.cost_d = c;
+  }
   const long long pairs = (long long)s.batch * s.kv_heads;
   t.total_tiles = pairs * t.tiles_per_pair;
+  t.pair_cost = (long long)t.packed_tiles * t.cost_q + (long long)dense_tiles * t.cost_d;
+  if (t.pair_cost < 1) t.pair_cost = 1;
+  t.total_cost = pairs * t.pair_cost;
+  if (t.total_cost >= (1LL << 32)) return mz_fail(MZ_ERR_UNSUPPORTED, "cache too large for the tiled kernel");
   long long W;
   if (splits_request > 0) {
     W = pairs * splits_request;
   } else {
     W = (long long)sm_count * warps;              // one resident CTA per SM
-    if (W > t.total_tiles / 2) W = t.total_tiles / 2;   // at least two tiles per warp
+    const long long two_tiles = t.total_cost / (2 * t.cost_q);   // at least two packed tiles' worth per warp
+    if (W > two_tiles) W = two_tiles;
     if (W < 1) W = 1;
   }
   if (W > (1LL << 30)) return mz_fail(MZ_ERR_ARG, "too many splits");
   t.total_warps = (int)W;
   t.ctas = (int)((W + warps - 1) / warps);
-  const long long len = (t.total_tiles + W - 1) / W;
-  t.max_segs = (int)((len + t.tiles_per_pair - 2) / t.tiles_per_pair + 1);
-  if (t.max_segs < 1) t.max_segs = 1;
+  // a warp's tiles start inside a cost interval of at most total_cost/W + 1
+  const long long len = t.total_cost / W + 2;
+  t.max_segs = (int)((len - 1) / t.pair_cost + 2);
   *slots = (size_t)W * t.max_segs * p.gqa;
   return MZ_OK;
 }

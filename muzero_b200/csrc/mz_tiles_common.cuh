@@ -10,9 +10,10 @@ constexpr float LOG2E = 1.4426950408889634f;
 // Lane mappings (one warp per tile of G tokens):
 //   keys   : 16 lanes share a row (one channel, G tokens), each lane owns TPL = G/16 consecutive
 //            tokens; the two half-warps take rows 2*step and 2*step+1            -> 64 steps
-//   values : 32 lanes share a token, each lane owns 4 consecutive channels       -> G steps
-// so one shared-memory lookup instruction touches at most two codebooks (keys) / NG codebooks
-// (values): with 16-entry books two of them cover the 32 banks exactly once, no conflicts.
+//   values : 16 lanes share a token, each lane owns TPL consecutive channels of every group; the
+//            two half-warps take tokens 2*step and 2*step+1                      -> G/2 steps
+// so one shared-memory lookup instruction touches two codebooks: with 16-entry books they cover
+// the 32 banks exactly once, no conflicts.
 template <int BITS, int G, int GQA>
 struct Cfg {
   static constexpr int NE = 1 << BITS;             // codebook entries
@@ -21,27 +22,39 @@ struct Cfg {
   static constexpr int NG = D / G;                 // value groups per token
   static constexpr int VROW_BYTES = 16 * BITS;     // packed bytes of one token's 128 value codes
   static constexpr int TILE_BYTES = D * QB;        // packed bytes of a key tile == of a value tile
+  // staging buffer of one side; a residual tile is DT un-quantized tokens (256 bytes each) in the same buffer
+  static constexpr int STAGE_BYTES = TILE_BYTES > 4096 ? TILE_BYTES : 4096;
+  static constexpr int DT = STAGE_BYTES / (2 * D);
   static constexpr bool BOOKS = BITS <= 4;         // per-row codebooks; wider codes are expanded arithmetically
   static constexpr int BOOK_STRIDE = !BOOKS ? 8 : (NE < 4 ? 4 : NE);   // floats per row
   static constexpr int ROW_BYTES = BOOK_STRIDE * 4;
   static constexpr int KSTEPS = D / 2;             // key steps per tile
-  static constexpr int VSTEPS = G;                 // value steps per tile
   static constexpr int UNROLL = 4;
+  // warps per CTA the kernel is compiled for: 8 heads per kv head hold twice the accumulators, and get
+  // the registers of a 256-thread block
+  static constexpr int MAX_WARPS = GQA > 4 ? 8 : 12;
   static constexpr int ROUNDS = (GQA + 1) / 2;     // softmax rounds: half-warp dl owns head 2*r + dl in round r
   static constexpr int META_BYTES = 1024;          // 2 x 128 entries x up to 4 bytes
   // 4-bit codes, 256-byte aligned lane blocks: the address of a lookup is one byte permute
   static constexpr bool PRMT_ADDR = BITS == 4;
+  // the expansion rows of a tile side are built and used in PASSES parts, so they never take more than 4 KB
+  static constexpr int PASSES = D * ROW_BYTES > 4096 ? 2 : 1;
+  static constexpr int RP = D / PASSES;            // rows per pass
+  static constexpr int TP = G / PASSES;            // value tokens per pass
   // per-warp shared memory, in bytes
-  static constexpr int BOOK_BYTES = D * ROW_BYTES;
-  static constexpr int KBUF = TILE_BYTES + META_BYTES;
-  static constexpr int VBUF = TILE_BYTES + META_BYTES;
+  static constexpr int BOOK_BYTES = RP * ROW_BYTES;
+  static constexpr int KBUF = STAGE_BYTES + META_BYTES;
+  static constexpr int VBUF = STAGE_BYTES + META_BYTES;
   static constexpr int PBUF = G * GQA * 4;         // probabilities [token][head]; also dense-key logits
   static constexpr int QBUF = D * GQA * 4;         // scaled query [channel][head]
   static constexpr int MISC = 64;
   static constexpr int PER_WARP = ((BOOK_BYTES + KBUF + VBUF + PBUF + QBUF + MISC + 255) / 256) * 256;
-  // per-CTA shared: two universal tables [NE][NE+1] float2 (keys, values) + slack to align to 256
-  static constexpr int UNIV_FLOAT2 = BOOKS ? NE * (NE + 1) : 0;
-  static constexpr int SHARED = ((2 * UNIV_FLOAT2 * 8 + 255) / 256) * 256 + 256;
+  // per-CTA shared: two shape tables (keys, values) [zero code][entry] of floats, rows padded by 4 floats
+  // so that the 16-byte reads of rows with different zero codes fall into different bank groups;
+  // + slack to align to 256
+  static constexpr int UROW = NE >= 4 ? NE + 4 : NE;
+  static constexpr int UNIV_FLOATS = BOOKS ? NE * UROW : 0;
+  static constexpr int SHARED = ((2 * UNIV_FLOATS * 4 + 255) / 256) * 256 + 256;
 };
 
 // ---- asynchronous copies (global -> shared, 16 bytes per lane per call) ----
