@@ -14,6 +14,7 @@ scales, q~N(0,1), seeded.
   value     tokens/s through the C ABI with all inputs resident in HBM
   e2e       tokens/s through the plug-in API (MuZeroCache.update + mu_zero_decode_attention_forward)
             with pinned host q/k/v copied in and the attention output copied out every step
+            (copies on a second stream, overlapped with the layers' kernels)
   roofline  algorithmic bytes of one decode-attention call / its mean duration (CUDA events on
             the launch stream, timed region only) against the measured HBM copy bandwidth
   cpu_baseline / --impl reference
@@ -44,9 +45,9 @@ LAYERS, BATCH, KVH, QH, CTX, RES, D, GROUP = 36, 64, 8, 32, 4096, 128, 128, 64
 NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_257_024 + 4_001_024) / 32
 
 
-def algorithmic_bytes(bits: int, batch=BATCH, sq=CTX, res=RES, meta=2, elem=2) -> int:
+def algorithmic_bytes(bits: int, batch=BATCH, sq=CTX, res=RES, meta=2, elem=2, group=GROUP) -> int:
     """Bytes one decode-attention call must move: packed codes + metadata + residual + q/out."""
-    per_pair = 2 * sq * D * bits // 8 + (sq // GROUP) * D * 2 * meta + sq * (D // GROUP) * 2 * meta + 2 * res * D * elem
+    per_pair = 2 * sq * D * bits // 8 + (sq // group) * D * 2 * meta + sq * (D // group) * 2 * meta + 2 * res * D * elem
     return batch * KVH * per_pair + 2 * batch * QH * D * elem
 
 
@@ -99,17 +100,17 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_layers(bits: int, device: torch.device, layers: int, batch: int, seed: int):
-    """`layers` caches holding CTX quantized + RES residual tokens each (values drawn on the device)."""
+def build_layers(bits: int, device: torch.device, layers: int, batch: int, seed: int, ctx: int = CTX, group: int = GROUP):
+    """`layers` caches holding `ctx` quantized + RES residual tokens each (values drawn on the device)."""
     import muzero_b200 as mz
     gen = torch.Generator(device=device).manual_seed(seed)
     chan = torch.exp(torch.randn(D, device=device, generator=gen))
     out = []
     for _ in range(layers):
-        layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=GROUP, residual_length=RES))
-        layer.max_cache_length = CTX + RES + 1024
-        k = (torch.randn(batch, KVH, CTX + RES, D, device=device, generator=gen) * chan).to(torch.bfloat16)
-        v = torch.randn(batch, KVH, CTX + RES, D, device=device, generator=gen).to(torch.bfloat16)
+        layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=group, residual_length=RES))
+        layer.max_cache_length = ctx + RES + 1024
+        k = (torch.randn(batch, KVH, ctx + RES, D, device=device, generator=gen) * chan).to(torch.bfloat16)
+        v = torch.randn(batch, KVH, ctx + RES, D, device=device, generator=gen).to(torch.bfloat16)
         layer.update(k, v, {"materialize_full_kv": False})
         del k, v
         out.append(layer)
@@ -208,23 +209,40 @@ def run_ours(args) -> dict:
     cache = mz.MuZeroCache(layers[0].cfg)
     cache.layers = layers
     module = SimpleNamespace(num_key_value_groups=QH // KVH)
-    host_q = [torch.randn(B, QH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
-    host_k = [torch.randn(B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
-    host_v = [torch.randn(B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    # the step's inputs (one q/k/v slice per layer) sit in pinned host memory; a copy stream uploads them
+    # slice by slice while the compute stream works on the layers whose slices have landed, and reads
+    # each layer's output back as soon as it exists.  Nothing of a later step is touched early.
+    host_q = [torch.randn(L, B, QH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    host_k = [torch.randn(L, B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    host_v = [torch.randn(L, B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
     host_out = torch.empty(L, B, 1, QH, D, dtype=torch.bfloat16).pin_memory()
-    h2d = L * (host_q[0].numel() + 2 * host_k[0].numel()) * 2
+    dev_q, dev_k, dev_v = (torch.empty_like(t[0], device=device) for t in (host_q, host_k, host_v))
+    h2d = (host_q[0].numel() + 2 * host_k[0].numel()) * 2
     d2h = host_out.numel() * 2
+    copy_stream = torch.cuda.Stream(device)
+    landed = [torch.cuda.Event() for _ in range(L)]
+    computed = [torch.cuda.Event() for _ in range(L)]
 
     def e2e_step(i: int):
+        compute = torch.cuda.current_stream()
+        with torch.cuda.stream(copy_stream):
+            for li in range(L):
+                dev_q[li].copy_(host_q[i & 1][li], non_blocking=True)
+                dev_k[li].copy_(host_k[i & 1][li], non_blocking=True)
+                dev_v[li].copy_(host_v[i & 1][li], non_blocking=True)
+                landed[li].record(copy_stream)
         outs = []
         for li in range(L):
-            dq = host_q[i & 1].to(device, non_blocking=True)
-            dk = host_k[i & 1].to(device, non_blocking=True)
-            dv = host_v[i & 1].to(device, non_blocking=True)
-            cache.update(dk, dv, li, {"materialize_full_kv": False})
-            out, _ = mz.mu_zero_decode_attention_forward(module, dq, None, D ** -0.5, cache.get_attention_state(li))
-            host_out[li].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()      # the step's result is on the host
+            compute.wait_event(landed[li])
+            cache.update(dev_k[li], dev_v[li], li, {"materialize_full_kv": False})
+            out, _ = mz.mu_zero_decode_attention_forward(module, dev_q[li], None, D ** -0.5, cache.get_attention_state(li))
+            computed[li].record(compute)
+            outs.append(out)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(computed[li])
+                host_out[li].copy_(out, non_blocking=True)
+        copy_stream.synchronize()                      # the step's result is on the host
+        compute.synchronize()
 
     for i in range(min(args.warmup, 3)):
         e2e_step(i)
@@ -275,7 +293,7 @@ def run_attention_only(args) -> dict:
     from muzero_b200.kernels._cabi import stream_ptr
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    layers = build_layers(args.bits, device, args.layers, args.batch, seed=1234)
+    layers = build_layers(args.bits, device, args.layers, args.batch, seed=1234, ctx=args.context, group=args.group)
     q = torch.randn(args.batch, QH, 1, D, device=device).to(torch.bfloat16)
     outs = [torch.empty(args.batch, 1, QH, D, dtype=torch.bfloat16, device=device) for _ in layers]
     cargs = [build_decode_args(l, q, D ** -0.5, None, o) for l, o in zip(layers, outs)]
@@ -292,9 +310,10 @@ def run_attention_only(args) -> dict:
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (args.steps * len(cargs))
-    abytes = algorithmic_bytes(args.bits, batch=args.batch)
+    abytes = algorithmic_bytes(args.bits, batch=args.batch, sq=args.context, group=args.group)
     peak, kind = measured_peak_gbs()
-    return {"mode": "attention-only", "bits": args.bits, "batch": args.batch, "layers": args.layers, "us_per_call": us,
+    return {"mode": "attention-only", "bits": args.bits, "batch": args.batch, "layers": args.layers, "context": args.context,
+            "group": args.group, "us_per_call": us,
             "bytes_per_call": abytes, "achieved_gbs": abytes / us / 1e3, "frac_of_peak": abytes / us / 1e3 / peak, "peak_kind": kind}
 
 
@@ -413,7 +432,8 @@ def main():
     ap.add_argument("--attention-only", action="store_true", help="small profiling case: only the fused attention calls")
     ap.add_argument("--generate", action="store_true", help="secondary workload: HF generate() on a Qwen3-8B shaped model")
     ap.add_argument("--cache", default="mu_zero", choices=["mu_zero", "dynamic"])
-    ap.add_argument("--context", type=int, default=CTX)
+    ap.add_argument("--context", type=int, default=CTX, help="quantized tokens per sequence (--attention-only, --generate)")
+    ap.add_argument("--group", type=int, default=GROUP, help="quantization group size (--attention-only)")
     ap.add_argument("--new-tokens", type=int, default=128)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -23,20 +23,31 @@ struct MzTilesPlan {
   // Work is cut into per-warp ranges by cost, not by tile count: a packed tile of G tokens costs
   // cost_q, a residual tile of dense_tokens un-quantized tokens costs cost_d.
   int packed_tiles, dense_tokens, cost_q, cost_d;
-  long long pair_cost, total_cost;   // packed_tiles*cost_q + dense_tiles*cost_d ; pairs * pair_cost
+  long long pair_cost, total_cost;   // packed_tiles*cost_q + dense_tiles*cost_d ; pairs * pair_cost (< 2^31)
+  unsigned cost_quot, cost_rem;      // total_cost / total_warps and the remainder
 };
 
 // Number of tiles (in flat order: pair-major, packed tiles before residual tiles) whose start cost
 // is below `c`.  Warp g owns the tiles [mz_tiles_before(g*total_cost/W), mz_tiles_before((g+1)*total_cost/W)).
-__host__ __device__ inline long long mz_tiles_before(const MzTilesPlan& t, long long c) {
-  const long long pair = c / t.pair_cost, r = c % t.pair_cost;
-  const long long qcost = (long long)t.packed_tiles * t.cost_q;
-  const long long in = r <= qcost ? (r + t.cost_q - 1) / t.cost_q : t.packed_tiles + (r - qcost + t.cost_d - 1) / t.cost_d;
-  return pair * t.tiles_per_pair + in;
+// total_cost < 2^31 (checked by the planner), so everything but g*total_cost fits 32 bits; with fewer
+// than 65536 warps that product is split as g*quot + g*rem/W and the whole computation uses 32-bit
+// divisions (a 64-bit division costs hundreds of cycles on the device).
+__host__ __device__ inline long long mz_tiles_before(const MzTilesPlan& t, unsigned c) {
+  const unsigned pc = (unsigned)t.pair_cost, cq = (unsigned)t.cost_q, cd = (unsigned)t.cost_d;
+  const unsigned pair = c / pc, r = c - pair * pc;
+  const unsigned qcost = (unsigned)t.packed_tiles * cq;
+  const unsigned in = r <= qcost ? (r + cq - 1) / cq : (unsigned)t.packed_tiles + (r - qcost + cd - 1) / cd;
+  return (long long)pair * t.tiles_per_pair + in;
+}
+__host__ __device__ inline unsigned mz_cost_at(const MzTilesPlan& t, long long g) {
+  if (t.total_warps < 65536) return (unsigned)g * t.cost_quot + (unsigned)g * t.cost_rem / (unsigned)t.total_warps;
+  return (unsigned)((unsigned long long)g * (unsigned long long)t.total_cost / (unsigned long long)t.total_warps);
 }
 __host__ __device__ inline void mz_warp_tiles(const MzTilesPlan& t, long long g, long long* f0, long long* f1) {
-  *f0 = mz_tiles_before(t, g * t.total_cost / t.total_warps);
-  *f1 = mz_tiles_before(t, (g + 1) * t.total_cost / t.total_warps);
+  const unsigned c0 = mz_cost_at(t, g);
+  *f0 = mz_tiles_before(t, c0);
+  if (g + 1 >= t.total_warps) { *f1 = t.total_tiles; return; }
+  *f1 = mz_tiles_before(t, mz_cost_at(t, g + 1));
 }
 
 struct MzDecodeParams {

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_t
   };
 
   Cursor cur;
-  cur.pair = (int)(f0 / T); cur.tile = (int)(f0 % T);
+  cur.pair = (int)((unsigned)f0 / (unsigned)T); cur.tile = (int)((unsigned)f0 % (unsigned)T);
   cur.b = cur.pair / s.kv_heads; cur.kvh = cur.pair % s.kv_heads;
   Cursor nxt = cur;
   stage_k(cur, true);
@@ -529,22 +529,40 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
   const int pair = blockIdx.x;
   const int W = p.tp.total_warps, T = p.tp.tiles_per_pair, gqa = p.gqa;
   const long long lo = (long long)pair * T, hi = lo + T;
-  if (threadIdx.x == 0) {
-    // first warp whose range reaches into this pair: start from the cost estimate, then settle
-    long long g = (long long)pair * p.tp.pair_cost * W / p.tp.total_cost, f0, f1;
-    if (g >= W) g = W - 1;
-    for (mz_warp_tiles(p.tp, g, &f0, &f1); g > 0 && f0 > lo; mz_warp_tiles(p.tp, g, &f0, &f1)) --g;
-    for (; g + 1 < W && f1 <= lo; mz_warp_tiles(p.tp, g, &f0, &f1)) ++g;
-    s_first = g;
-    int n = 0;
-    for (long long gw = g; gw < W; ++gw) {
+  if (threadIdx.x < 32) {
+    // Which warps of the main kernel hold records of this pair?  They are consecutive.  The 32 lanes test
+    // a window of candidates around the cost estimate at once; only if the window might not cover all of
+    // them (it reaches an end that could continue, or finds none) lane 0 walks the warps one by one.
+    const int lane = threadIdx.x;
+    const long long g_est = (unsigned)pair * (unsigned)p.tp.pair_cost / (p.tp.cost_quot ? p.tp.cost_quot : 1u);
+    const long long g0 = g_est - 3, gw = g0 + lane;
+    long long f0 = 0, f1 = 0;
+    bool on = false;
+    if (gw >= 0 && gw < W) {
       mz_warp_tiles(p.tp, gw, &f0, &f1);
-      if (f0 >= hi) break;
-      if (f1 <= lo || f0 >= f1) continue;
-      if (n < kMaxCombineSlots) s_slot[n] = gw * p.tp.max_segs + (pair - (int)(f0 / T));
-      ++n;
+      on = f0 < hi && f1 > lo && f0 < f1;
     }
-    s_n = n;
+    const unsigned mask = __ballot_sync(0xffffffffu, on);
+    const bool open = mask == 0 || ((mask & 1u) && g0 > 0) || ((mask >> 31) && g0 + 31 < W - 1);
+    if (!open) {
+      if (on) s_slot[__popc(mask & ((1u << lane) - 1u))] = gw * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T));
+      if (lane == 0) { s_n = __popc(mask); s_first = g0 + __ffs(mask) - 1; }
+    } else if (lane == 0) {
+      long long g = g_est;
+      if (g >= W) g = W - 1;
+      for (mz_warp_tiles(p.tp, g, &f0, &f1); g > 0 && f0 > lo; mz_warp_tiles(p.tp, g, &f0, &f1)) --g;
+      for (; g + 1 < W && f1 <= lo; mz_warp_tiles(p.tp, g, &f0, &f1)) ++g;
+      s_first = g;
+      int n = 0;
+      for (long long gx = g; gx < W; ++gx) {
+        mz_warp_tiles(p.tp, gx, &f0, &f1);
+        if (f0 >= hi) break;
+        if (f1 <= lo || f0 >= f1) continue;
+        if (n < kMaxCombineSlots) s_slot[n] = gx * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T));
+        ++n;
+      }
+      s_n = n;
+    }
   }
   __syncthreads();
   const int n = s_n;
@@ -559,22 +577,47 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
         mz_warp_tiles(p.tp, gw, &f0, &f1);
         if (f0 >= hi) break;
         if (f1 <= lo || f0 >= f1) continue;
-        fn(gw * p.tp.max_segs + (pair - (int)(f0 / T)));
+        fn(gw * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T)));
       }
     }
   };
   for (int h = threadIdx.x >> 7; h < gqa; h += blockDim.x >> 7) {
     const int d = threadIdx.x & 127;
-    float mx = -INFINITY;
-    for_each_slot([&](long long sl) { mx = fmaxf(mx, p.part.m[sl * gqa + h]); });
-    float lsum = 0.f, a = 0.f;
-    for_each_slot([&](long long sl) {
-      const long long slot = sl * gqa + h;
-      const float mi = p.part.m[slot];
-      const float wgt = mi > -INFINITY ? __expf(mi - mx) : 0.f;
-      lsum = fmaf(p.part.l[slot], wgt, lsum);
-      a = fmaf(p.part.acc[slot * D + d], wgt, a);
-    });
+    float mx = -INFINITY, lsum = 0.f, a = 0.f;
+    if (listed) {
+      // four records at a time: their loads are independent and in flight together; the running
+      // maximum is carried along (one pass)
+      for (int i0 = 0; i0 < n; i0 += 4) {
+        float mi[4], li[4], ai[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const bool on = i0 + j < n;
+          const long long slot = on ? s_slot[i0 + j] * gqa + h : 0;
+          mi[j] = on ? p.part.m[slot] : -INFINITY;
+          li[j] = on ? p.part.l[slot] : 0.f;
+          ai[j] = on ? p.part.acc[slot * D + d] : 0.f;
+        }
+        const float m_new = fmaxf(fmaxf(mx, fmaxf(mi[0], mi[1])), fmaxf(mi[2], mi[3]));
+        const float keep = mx > -INFINITY ? __expf(mx - m_new) : 0.f;
+        lsum *= keep; a *= keep;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float wgt = mi[j] > -INFINITY ? __expf(mi[j] - m_new) : 0.f;
+          lsum = fmaf(li[j], wgt, lsum);
+          a = fmaf(ai[j], wgt, a);
+        }
+        mx = m_new;
+      }
+    } else {
+      for_each_slot([&](long long sl) { mx = fmaxf(mx, p.part.m[sl * gqa + h]); });
+      for_each_slot([&](long long sl) {
+        const long long slot = sl * gqa + h;
+        const float mi = p.part.m[slot];
+        const float wgt = mi > -INFINITY ? __expf(mi - mx) : 0.f;
+        lsum = fmaf(p.part.l[slot], wgt, lsum);
+        a = fmaf(p.part.acc[slot * D + d], wgt, a);
+      });
+    }
     const long long row = (long long)pair * gqa + h;
     if (o.out) mz_store_from_float(o.out, row * D + d, a / fmaxf(lsum, 1e-20f), o.out_dt);
     else {
@@ -700,7 +743,7 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
   t.pair_cost = (long long)t.packed_tiles * t.cost_q + (long long)dense_tiles * t.cost_d;
   if (t.pair_cost < 1) t.pair_cost = 1;
   t.total_cost = pairs * t.pair_cost;
-  if (t.total_cost >= (1LL << 32)) return mz_fail(MZ_ERR_UNSUPPORTED, "cache too large for the tiled kernel");
+  if (t.total_cost >= (1LL << 31)) return mz_fail(MZ_ERR_UNSUPPORTED, "cache too large for the tiled kernel");
   long long W;
   if (splits_request > 0) {
     W = pairs * splits_request;
@@ -712,6 +755,8 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
   }
   if (W > (1LL << 30)) return mz_fail(MZ_ERR_ARG, "too many splits");
   t.total_warps = (int)W;
+  t.cost_quot = (unsigned)(t.total_cost / W);
+  t.cost_rem = (unsigned)(t.total_cost % W);
   t.ctas = (int)((W + warps - 1) / warps);
   // a warp's tiles start inside a cost interval of at most total_cost/W + 1
   const long long len = t.total_cost / W + 2;
