@@ -530,9 +530,9 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
   const int W = p.tp.total_warps, T = p.tp.tiles_per_pair, gqa = p.gqa;
   const long long lo = (long long)pair * T, hi = lo + T;
   if (threadIdx.x < 32) {
-    // Which warps of the main kernel hold records of this pair?  They are consecutive.  The 32 lanes test
-    // a window of candidates around the cost estimate at once; only if the window might not cover all of
-    // them (it reaches an end that could continue, or finds none) lane 0 walks the warps one by one.
+    // Which warps of the main kernel hold records of this pair?  The 32 lanes test a window of candidates
+    // around the cost estimate at once; only if the window's tile span does not cover the pair, lane 0
+    // walks the warps one by one.
     const int lane = threadIdx.x;
     const long long g_est = (unsigned)pair * (unsigned)p.tp.pair_cost / (p.tp.cost_quot ? p.tp.cost_quot : 1u);
     const long long g0 = g_est - 3, gw = g0 + lane;
@@ -543,7 +543,10 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
       on = f0 < hi && f1 > lo && f0 < f1;
     }
     const unsigned mask = __ballot_sync(0xffffffffu, on);
-    const bool open = mask == 0 || ((mask & 1u) && g0 > 0) || ((mask >> 31) && g0 + 31 < W - 1);
+    // warp ranges are consecutive, so the window spans [f0 of its first warp, f1 of its last warp)
+    const int first_lane = g0 < 0 ? (int)-g0 : 0, last_lane = g0 + 31 > W - 1 ? (int)(W - 1 - g0) : 31;
+    const int w_lo = __shfl_sync(0xffffffffu, (int)f0, first_lane & 31), w_hi = __shfl_sync(0xffffffffu, (int)f1, last_lane & 31);
+    const bool open = first_lane > 31 || last_lane < 0 || w_lo > lo || w_hi < hi;
     if (!open) {
       if (on) s_slot[__popc(mask & ((1u << lane) - 1u))] = gw * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T));
       if (lane == 0) { s_n = __popc(mask); s_first = g0 + __ffs(mask) - 1; }

@@ -132,3 +132,19 @@ def test_expand_table_host_equals_oracle(oracle):
     from muzero_b200.kernels.loader import expand_table_host
     for bits in (1, 4, 8):
         assert torch.equal(expand_table_host(bits, 2.0), oracle.expand_table_oracle(bits, 2.0))
+
+
+def test_tile_partition_matches_bruteforce(tmp_path):
+    """The decode kernel and its merge kernel find each warp's tiles with the same 32-bit functions
+    (muzero_b200/csrc/mz_decode.cuh); they must agree with plain 64-bit arithmetic and tile the list."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    exe = tmp_path / "partition_check"
+    src = os.path.join(os.path.dirname(__file__), "partition_check.cu")
+    subprocess.run([nvcc, "-std=c++17", "-o", str(exe), src], check=True, capture_output=True)
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout
+    assert "BAD" not in run.stdout and run.stdout.count(": ok") == 12
