@@ -40,9 +40,9 @@ sys.path.insert(0, ROOT)
 
 LAYERS, BATCH, KVH, QH, CTX, RES, D, GROUP = 36, 64, 8, 32, 4096, 128, 128, 64
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_tiles_kernel launch at 4 bits, per sequence, from the
-# ncu capture summarised in profiles/decode_tiles_4bit_b32.md (batch 32: 168.26 MB + 4.00 MB); traffic is
+# ncu capture summarised in profiles/decode_tiles_4bit_b32.md (batch 32: 168.13 MB + 4.04 MB); traffic is
 # proportional to the batch, so a batch-64 launch is twice the captured one.
-NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_257_024 + 4_001_024) / 32
+NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_129_792 + 4_042_240) / 32
 
 
 def algorithmic_bytes(bits: int, batch=BATCH, sq=CTX, res=RES, meta=2, elem=2, group=GROUP) -> int:
