@@ -210,8 +210,8 @@ def run_ours(args) -> dict:
     cache.layers = layers
     module = SimpleNamespace(num_key_value_groups=QH // KVH)
     # the step's inputs (one q/k/v slice per layer) sit in pinned host memory; a copy stream uploads them
-    # slice by slice while the compute stream works on the layers whose slices have landed, and reads
-    # each layer's output back as soon as it exists.  Nothing of a later step is touched early.
+    # slice by slice while the compute stream works on the layers whose slices have landed, and a third
+    # stream reads each layer's output back as soon as it exists.  Nothing of a later step is touched early.
     host_q = [torch.randn(L, B, QH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
     host_k = [torch.randn(L, B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
     host_v = [torch.randn(L, B, KVH, 1, D).to(torch.bfloat16).pin_memory() for _ in range(2)]
@@ -219,29 +219,29 @@ def run_ours(args) -> dict:
     dev_q, dev_k, dev_v = (torch.empty_like(t[0], device=device) for t in (host_q, host_k, host_v))
     h2d = (host_q[0].numel() + 2 * host_k[0].numel()) * 2
     d2h = host_out.numel() * 2
-    copy_stream = torch.cuda.Stream(device)
+    copy_stream = torch.cuda.Stream(device)          # host -> device
+    back_stream = torch.cuda.Stream(device)          # device -> host
     landed = [torch.cuda.Event() for _ in range(L)]
     computed = [torch.cuda.Event() for _ in range(L)]
 
     def e2e_step(i: int):
         compute = torch.cuda.current_stream()
-        with torch.cuda.stream(copy_stream):
-            for li in range(L):
+        outs = []
+        for li in range(L):
+            with torch.cuda.stream(copy_stream):
                 dev_q[li].copy_(host_q[i & 1][li], non_blocking=True)
                 dev_k[li].copy_(host_k[i & 1][li], non_blocking=True)
                 dev_v[li].copy_(host_v[i & 1][li], non_blocking=True)
                 landed[li].record(copy_stream)
-        outs = []
-        for li in range(L):
             compute.wait_event(landed[li])
             cache.update(dev_k[li], dev_v[li], li, {"materialize_full_kv": False})
             out, _ = mz.mu_zero_decode_attention_forward(module, dev_q[li], None, D ** -0.5, cache.get_attention_state(li))
             computed[li].record(compute)
             outs.append(out)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(computed[li])
+            with torch.cuda.stream(back_stream):
+                back_stream.wait_event(computed[li])
                 host_out[li].copy_(out, non_blocking=True)
-        copy_stream.synchronize()                      # the step's result is on the host
+        back_stream.synchronize()                      # the step's result is on the host
         compute.synchronize()
 
     for i in range(min(args.warmup, 3)):

@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_t
   extern __shared__ __align__(16) uint8_t smem[];
   const mz_kv_store& s = p.s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the merge kernel waits for this grid's completion itself
 
   // signed shape tables: row zc, entry e -> normalised value of code e (>= 0 at and above the zero code, < 0 below)
   uint8_t* smem_al = smem + ((256u - ((unsigned)__cvta_generic_to_shared(smem) & 255u)) & 255u);
@@ -567,6 +568,8 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
       s_n = n;
     }
   }
+  // everything above is arithmetic on the plan; the records themselves are the main kernel's output
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncthreads();
   const int n = s_n;
   const bool listed = n <= kMaxCombineSlots;
@@ -790,7 +793,19 @@ int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st) {
 
 int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t st) {
   if (p.tp.max_segs < 1) return mz_fail(MZ_ERR_ARG, "bad plan");
-  mzt::combine_tiles_kernel<<<(unsigned)(p.s.batch * p.s.kv_heads), 128 * (p.gqa < 4 ? p.gqa : 4), 0, st>>>(p, o);
+  // programmatic dependent launch: the merge grid may start while the main kernel drains; it finds its
+  // records (pure arithmetic) and then waits for the main grid's results (griddepcontrol.wait)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.s.batch * p.s.kv_heads));
+  cfg.blockDim = dim3(128 * (p.gqa < 4 ? p.gqa : 4));
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_kernel, p, o));
   MZ_LAUNCH_CHECK("combine_tiles");
   return MZ_OK;
 }

@@ -222,3 +222,32 @@ def test_long_context_many_warps(oracle):
     want = oracle.decode_attention_oracle(q, ref, 128 ** -0.5, 4, compute_dtype=torch.float32)
     got = decode_attention(layer, q.cuda(), 128 ** -0.5, out_dtype=torch.float32)
     assert (got.cpu() - want).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("bits,group,gqa", [(4, 128, 8), (4, 32, 4), (2, 128, 2), (3, 64, 1)])
+def test_masks_over_residual_tiles_and_wide_groups(oracle, bits, group, gqa):
+    """Additive mask reaching into packed tiles and into the ragged last residual tile, for tile shapes
+    other than the headline one (two-pass codebooks at G=128, 8 heads per kv head, 1 head)."""
+    from muzero_b200.cache.attention import decode_attention
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 3, 2, 2 * gqa, 700, 128, bits, group, 128, seed=bits + group + gqa, steps=5)
+    total = 705
+    mask = torch.zeros(3, 1, 1, total)
+    mask[0, ..., :70] = torch.finfo(torch.bfloat16).min
+    mask[1, ..., 560:650] = -4.0
+    mask[2, ..., 690:] = torch.finfo(torch.bfloat16).min
+    want = oracle.decode_attention_oracle(q, ref, 0.09, gqa, mask=mask, compute_dtype=torch.float32)
+    got = decode_attention(layer, q.cuda(), 0.09, mask.cuda(), out_dtype=torch.float32)
+    assert (got.cpu() - want).abs().max().item() <= TOL
+
+
+def test_many_pairs_and_split_counts_beyond_16_bits(oracle):
+    """24 (batch, kv head) pairs: warps cross pair boundaries inside packed and residual tiles.  Then a split
+    count that makes more than 65535 warps (the 64-bit branch of the tile partition) must give the same result."""
+    from muzero_b200.cache.attention import decode_attention
+    ref, layer, q = _oracle_and_gpu_layers(oracle, 6, 4, 16, 700, 128, 4, 64, 128, seed=606, steps=2)
+    want = oracle.decode_attention_oracle(q, ref, 0.09, 4, compute_dtype=torch.float32)
+    got = decode_attention(layer, q.cuda(), 0.09, out_dtype=torch.float32)
+    assert (got.cpu() - want).abs().max().item() <= TOL
+    for splits in (3, 17, 3000):          # 24 * 3000 = 72,000 warps
+        again = decode_attention(layer, q.cuda(), 0.09, out_dtype=torch.float32, splits=splits)
+        assert (again - got).abs().max().item() < 2e-5, splits
