@@ -163,6 +163,27 @@ size_t mz_decode_workspace_bytes(const mz_decode_args* args);
 int mz_decode_attention(const mz_decode_args* args, void* stream);
 
 /*
+ * One decode step of one layer in a single call: mz_append_kv of the new token, then -- when the
+ * residual window exceeds `residual_length` by at least `flush_unit` tokens (a multiple of the group
+ * size: one group, or four in the reference's default decode mode) -- mz_flush_kv of
+ * floor(excess / flush_unit) * flush_unit oldest tokens, then mz_decode_attention.  The counters of
+ * args->store (k_groups, v_tokens, res_start, res_len) are advanced in place; the caller mirrors them.
+ * Capacities are the caller's: `window_capacity` rows behind store.res_k/res_v, `group_capacity` key
+ * groups (and group_capacity * group value tokens) in the packed store; MZ_ERR_WORKSPACE, with nothing
+ * launched, when the step would not fit.  alpha_key / alpha_value must already be chosen.
+ * Replaces the per-token host sequence MuZeroCacheLayer.update -> compress_residual_prefix ->
+ * mu_zero_decode_attention_forward, muzero/cache/layer.py:407-459,369-401 and
+ * muzero/cache/attention.py:48-295 (callers: muzero/integrations/transformers_patch.py:529-592).
+ */
+int mz_decode_step(mz_decode_args* args, const void* k_new, const void* v_new, long long new_stride_b,
+                   long long new_stride_h, int residual_length, int flush_unit, int group_capacity,
+                   int window_capacity, float eps, void* stream);
+
+/* Bytes of workspace mz_decode_step needs: those of mz_decode_attention on the store as it will be
+ * after the append and the flush of the step (0 on invalid arguments). */
+size_t mz_decode_step_workspace_bytes(const mz_decode_args* args, int residual_length, int flush_unit);
+
+/*
  * Decode attention for callers that cannot allocate device memory.
  * (No counterpart in the reference: its kernels always receive torch-allocated buffers.)
  *

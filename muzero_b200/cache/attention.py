@@ -42,8 +42,11 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 
 def build_decode_args(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor],
-                      out: Optional[torch.Tensor], *, splits: int = 0) -> DecodeArgs:
-    """Fills the C argument block for one decode call on ``layer``."""
+                      out: Optional[torch.Tensor], *, splits: int = 0, step: Optional[tuple[int, int]] = None) -> DecodeArgs:
+    """Fills the C argument block for one decode call on ``layer``.
+
+    ``step=(residual_length, flush_unit)``: the block is for ``mz_decode_step``, i.e. the mask must
+    cover one more token and the workspace is sized for the store as it will be after the step."""
     if not query.is_cuda:
         raise MuZeroKernelError("decode attention needs CUDA tensors; this package has no CPU path")
     if query.dtype != layer.dtype:
@@ -64,7 +67,7 @@ def build_decode_args(layer, query: torch.Tensor, scaling: float, attention_mask
             mask = mask.to(query.dtype)
         if mask.dtype not in (torch.float32, torch.float16, torch.bfloat16):
             mask = mask.to(torch.float32)
-        total = a.store.k_groups * a.store.group + a.store.res_len
+        total = a.store.k_groups * a.store.group + a.store.res_len + (1 if step else 0)
         if mask.dim() != 4 or mask.shape[1] != 1 or mask.shape[2] != 1 or mask.shape[-1] < total:
             raise MuZeroKernelError(f"attention_mask must be [B,1,1,>={total}], got {tuple(mask.shape)}")
         if mask.stride(-1) != 1:
@@ -78,7 +81,10 @@ def build_decode_args(layer, query: torch.Tensor, scaling: float, attention_mask
         a.out = out.data_ptr()
         a.out_dtype = dtype_code(out.dtype)
     lib = load_mu_zero_cuda_extension()
-    need = lib.mz_decode_workspace_bytes(ctypes.byref(a))
+    if step:
+        need = lib.mz_decode_step_workspace_bytes(ctypes.byref(a), int(step[0]), int(step[1]))
+    else:
+        need = lib.mz_decode_workspace_bytes(ctypes.byref(a))
     if need == 0:   # the size query validates like the call does and leaves its message behind
         raise MuZeroKernelError(f"invalid decode-attention arguments: {last_error()}")
     ws = _workspace(query.device, need)
@@ -124,6 +130,24 @@ def lse_merge(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, out_dtype: to
                                                          out.data_ptr(), dtype_code(out_dtype), stream_ptr(acc.device)),
               "mz_lse_merge")
     return out
+
+
+def mu_zero_decode_step_forward(module, layer, key_states: torch.Tensor, value_states: torch.Tensor, query: torch.Tensor,
+                                attention_mask, scaling: float):
+    """The patched model forwards' decode step: ``layer.update`` of the new token followed by
+    ``mu_zero_decode_attention_forward``, done by ``MuZeroCacheLayer.decode_step`` in one C call when
+    the cache is in its steady state.  Returns ``(attn_output [B,1,H,D], None)`` and keeps the statistics."""
+    _MU_ZERO_DECODE_STATS["calls"] += 1
+    groups = getattr(module, "num_key_value_groups", None)
+    if groups is not None and query.shape[1] != groups * key_states.shape[1]:
+        raise MuZeroKernelError("query heads do not match num_key_value_groups * kv heads")
+    out = layer.decode_step(key_states, value_states, query, scaling, attention_mask)
+    if layer._key_group_count > 0:
+        _MU_ZERO_DECODE_STATS["fused_qk_success"] += 1
+        _MU_ZERO_DECODE_STATS["fused_av_success"] += 1
+        _MU_ZERO_DECODE_STATS["fused_prefix_decode_success"] += 1
+    _MU_ZERO_DECODE_STATS["returns"] += 1
+    return out, None
 
 
 def mu_zero_decode_attention_forward(module, query: torch.Tensor, attention_mask, scaling: float,

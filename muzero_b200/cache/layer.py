@@ -338,6 +338,55 @@ class MuZeroCacheLayer:
         return (torch.cat([self._dequantize_key_prefix(), self.keys], dim=2),
                 torch.cat([self._dequantize_value_prefix(), self.values], dim=2))
 
+    def decode_step(self, key_states: torch.Tensor, value_states: torch.Tensor, query: torch.Tensor, scaling: float,
+                    attention_mask: torch.Tensor | None = None) -> torch.Tensor:
+        """One decode step: append ``[B,KVH,1,D]`` K/V, flush when due, attend with ``query [B,H,1,D]``.
+
+        Equivalent to ``update(..., {"materialize_full_kv": False})`` followed by the fused decode
+        attention (reference: muzero/cache/layer.py:407-459 and muzero/cache/attention.py:48-295), but in the
+        steady state (window inside its buffer, store with room, alphas chosen) it is a single C call,
+        ``mz_decode_step``.  Anything else takes the two-call route.  Returns ``[B,1,H,D]``."""
+        from .attention import build_decode_args, decode_attention
+        g = self.q_group_size
+        fast = (self.is_initialized and self._key_buffer is not None and key_states.shape[2] == 1 and key_states.is_cuda
+                and key_states.dtype == self.dtype and not self.cfg.logq_compatible_layout
+                and key_states.stride(-1) == 1 and value_states.stride(-1) == 1
+                and key_states.stride()[:2] == value_states.stride()[:2])
+        unit = g if self.cfg.decode_flush_by_group else 4 * g
+        if fast:
+            cur = int(self.keys.shape[2])
+            if self._res_start + cur + 1 > self._buffer_capacity:
+                fast = False                      # the window has to move back to the front of its buffer
+            excess = cur + 1 - self.residual_length
+            n = (excess // unit) * unit if excess > 0 else 0
+            if fast and n > 0:
+                if self._selected_alpha_key is None or self._selected_alpha_value is None:
+                    fast = False                  # the first flush chooses the alphas from the data
+                else:
+                    self._ensure_store(self._key_group_count + n // g, self._value_storage_len + n)
+        if not fast:
+            self.update(key_states, value_states, {"materialize_full_kv": False})
+            return decode_attention(self, query, scaling, attention_mask)
+        b, h, _, d = query.shape
+        out = torch.empty((b, 1, h, d), dtype=query.dtype, device=query.device)
+        args = build_decode_args(self, query, scaling, attention_mask, out, step=(self.residual_length, unit))
+        with torch.cuda.device(self.device):
+            check(load_mu_zero_cuda_extension().mz_decode_step(
+                ctypes.byref(args), key_states.data_ptr(), value_states.data_ptr(), key_states.stride(0), key_states.stride(1),
+                self.residual_length, unit, int(self._bufs["pk"].shape[2]) if self._bufs else 0,
+                self._buffer_capacity - self._res_start, self.amax_eps, stream_ptr(self.device)), "mz_decode_step")
+        st = args.store
+        flushed = st.k_groups != self._key_group_count
+        self._res_start += st.res_start            # the descriptor's window starts at its own pointer
+        self._key_group_count, self._value_storage_len = st.k_groups, st.v_tokens
+        a = self._res_start
+        self.keys = self._key_buffer[:, :, a:a + st.res_len]
+        self.values = self._value_buffer[:, :, a:a + st.res_len]
+        self.cumulative_length += 1
+        if flushed:
+            self._refresh_views()
+        return out
+
     def get_attention_state(self) -> dict[str, Any] | None:
         if not self.is_initialized:
             return None

@@ -11,6 +11,7 @@
 template <int DT>
 struct MzQuantRow {
   float lo, span, anchor, zero_code, steps_up, steps_dn, room_up, room_dn;
+  float inv_span, inv_up, inv_dn;   // correctly rounded reciprocals of the three per-row divisors
   float alpha, log_base, top;
   const uint16_t* __restrict__ ctab;
   int ctab_n;
@@ -34,6 +35,22 @@ struct MzQuantRow {
     steps_dn = fmaxf(zero_code, 1.0f);
     room_up = fmaxf(TT::round(__fsub_rn(1.0f, anchor)), eps_t);
     room_dn = fmaxf(anchor, eps_t);
+    inv_span = __frcp_rn(span);
+    inv_up = __frcp_rn(room_up);
+    inv_dn = __frcp_rn(room_dn);
+  }
+
+  // round_T(num / den) for a per-row divisor `den` with inv = RN(1/den).  bf16: num*inv is within 1.5
+  // fp32 ulps of the correctly rounded fp32 quotient, and the two round to the same bf16 value unless a
+  // bf16 rounding boundary (low half-word 0x8000) lies that close; only then the IEEE division is
+  // done.  Other types take the division.
+  __device__ __forceinline__ float quotient(float num, float den, float inv) const {
+    if (DT == MZ_BF16) {
+      const float y = __fmul_rn(num, inv);
+      const uint32_t low = __float_as_uint(y) & 0xffffu;
+      if (low - 0x7ffcu > 8u) return TT::round(y);
+    }
+    return TT::round(__fdiv_rn(num, den));
   }
 
   // round_T(round_T(log1p(round_T(alpha*p))) / log_base) for p in [0,1]
@@ -53,13 +70,13 @@ struct MzQuantRow {
   __device__ __forceinline__ int code(float x) const {
     // NaN (0/0 when the row range or a side extent rounds to zero in T) propagates through the
     // reference's chain and its final cast to uint8 yields 0; mirror that outcome.
-    float unit = TT::round(__fdiv_rn(TT::round(__fsub_rn(x, lo)), span));
+    float unit = quotient(TT::round(__fsub_rn(x, lo)), span, inv_span);
     if (unit != unit || anchor != anchor) return 0;
     unit = fminf(fmaxf(unit, 0.0f), 1.0f);
     // one path for both sides of the zero anchor (lanes of a warp straddle it): round(a-b) == -round(b-a)
     const bool up = unit >= anchor;
     const float num = fabsf(TT::round(__fsub_rn(unit, anchor)));
-    float p = TT::round(__fdiv_rn(num, up ? room_up : room_dn));
+    float p = quotient(num, up ? room_up : room_dn, up ? inv_up : inv_dn);
     if (p != p) return 0;
     p = fminf(fmaxf(p, 0.0f), 1.0f);
     const float rr = rintf(TT::round(__fmul_rn(compand(p), up ? steps_up : steps_dn)));

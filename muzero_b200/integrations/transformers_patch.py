@@ -16,7 +16,7 @@ from typing import Any, Optional
 
 import torch
 
-from ..cache.attention import mu_zero_decode_attention_forward
+from ..cache.attention import mu_zero_decode_attention_forward, mu_zero_decode_step_forward
 from ..cache.layer import MuZeroCacheLayer
 from ..config import SUPPORTED_BITS, MuZeroConfig
 
@@ -301,6 +301,13 @@ def _wrap_attention_forward(module, cls_name: str, qk_norm: bool) -> None:
             cache.finalize_prefill_quantization()
             cache.defer_prefill_quantization = False
         fused = single and os.environ.get("MUZERO_DISABLE_FUSED_DECODE", "0") != "1"
+        if fused and os.environ.get("MUZERO_DISABLE_DECODE_STEP", "0") != "1" and self.layer_idx < len(cache.layers):
+            # steady-state decode: append, flush when due and attention in one call into the library
+            if self.layer_idx == 0:
+                cache._seen_tokens += 1
+            out, weights = mu_zero_decode_step_forward(self, cache.layers[self.layer_idx], k, v, q, attention_mask, self.scaling)
+            out = out.reshape(*batch_shape, -1).contiguous()
+            return self.o_proj(out), weights
         k, v = cache.update(k, v, self.layer_idx, {
             "sin": sin, "cos": cos, "cache_position": kwargs.get("cache_position"),
             "materialize_full_kv": not fused,

@@ -143,3 +143,60 @@ def test_crop_reorder_offload(oracle):
     assert torch.equal(layer._full_kv()[0], full_k[[2, 0]])
     layer.crop(100)
     assert layer.get_seq_length() == 100 and torch.equal(layer.keys, full_k[[2, 0], :, :100])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("by_group,bits", [(True, 4), (False, 4), (True, 2)])
+def test_decode_step_equals_update_then_attention(oracle, by_group, bits):
+    """`MuZeroCacheLayer.decode_step` (one C call: append, flush when due, attention) against the two-call
+    route over 600 steps: same outputs bit for bit, same store, same residual window, across flushes,
+    store growth and the window sliding back to the front of its buffer."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
+    steps = 600
+    k, v, _ = oracle.synth_kv(2, 2, 300 + steps, 128, 8, seed=11 + bits)
+    gen = torch.Generator().manual_seed(5)
+    qs = torch.randn(steps, 2, 8, 1, 128, generator=gen).to(torch.bfloat16).cuda()
+    k, v = k.cuda(), v.cuda()
+    cfg = dict(bits=bits, q_group_size=64, residual_length=128, decode_flush_by_group=by_group)
+    a, b = mz.MuZeroCacheLayer(mz.MuZeroConfig(**cfg)), mz.MuZeroCacheLayer(mz.MuZeroConfig(**cfg))
+    for layer in (a, b):
+        layer.update(k[:, :, :300].contiguous(), v[:, :, :300].contiguous(), {"materialize_full_kv": False})
+    fast = 0
+    for i in range(steps):
+        kn, vn = k[:, :, 300 + i:301 + i], v[:, :, 300 + i:301 + i]
+        a.update(kn, vn, {"materialize_full_kv": False})
+        want = decode_attention(a, qs[i], 0.09)
+        before = b._res_start
+        got = b.decode_step(kn, vn, qs[i], 0.09)
+        fast += int(b._res_start >= before)
+        assert torch.equal(got, want), i
+        assert (b._key_group_count, b._value_storage_len, b.keys.shape[2], b.cumulative_length) == \
+               (a._key_group_count, a._value_storage_len, a.keys.shape[2], a.cumulative_length), i
+    assert torch.equal(a._packed_key_q, b._packed_key_q) and torch.equal(a._packed_value_q, b._packed_value_q)
+    assert torch.equal(a._key_mn, b._key_mn) and torch.equal(a._value_scale, b._value_scale)
+    assert torch.equal(a.keys, b.keys) and torch.equal(a.values, b.values)
+    assert a._key_group_count > 4 and fast > steps // 2
+
+
+@pytest.mark.gpu
+def test_decode_step_with_mask_and_refusals(oracle):
+    """Additive mask covering the token of the step; a mask that is one token short is refused."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
+    from muzero_b200.kernels._cabi import MuZeroKernelError
+    k, v, q = oracle.synth_kv(2, 2, 401, 128, 8, seed=3)
+    k, v, q = k.cuda(), v.cuda(), q.cuda()
+    a, b = mz.MuZeroCacheLayer(mz.MuZeroConfig()), mz.MuZeroCacheLayer(mz.MuZeroConfig())
+    for layer in (a, b):
+        layer.update(k[:, :, :399].contiguous(), v[:, :, :399].contiguous(), {"materialize_full_kv": False})
+        layer.update(k[:, :, 399:400], v[:, :, 399:400], {"materialize_full_kv": False})    # window now lives in its buffer
+    mask = torch.zeros(2, 1, 1, 401, device="cuda")
+    mask[0, ..., :50] = -1e4
+    mask[1, ..., 395:] = -2.0
+    a.update(k[:, :, 400:401], v[:, :, 400:401], {"materialize_full_kv": False})
+    want = decode_attention(a, q, 0.09, mask)
+    got = b.decode_step(k[:, :, 400:401], v[:, :, 400:401], q, 0.09, mask)
+    assert torch.equal(got, want)
+    with pytest.raises(MuZeroKernelError):
+        b.decode_step(k[:, :, 400:401], v[:, :, 400:401], q, 0.09, mask)      # 402 tokens now, mask has 401
