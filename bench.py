@@ -317,6 +317,69 @@ def run_attention_only(args) -> dict:
             "bytes_per_call": abytes, "achieved_gbs": abytes / us / 1e3, "frac_of_peak": abytes / us / 1e3 / peak, "peak_kind": kind}
 
 
+def run_kv_split(args) -> dict:
+    """Secondary workload (BASELINE config 4): one very long context split over the ranks' GPUs.  Each rank
+    holds a contiguous slice of `--context` quantized tokens (the last one also the residual window), computes
+    its partial (m, l, acc), the triples are all-gathered (NCCL) and merged on every rank.  Timed with CUDA
+    events around the whole call (partial + all-gather + merge), max over ranks."""
+    import torch.distributed as dist
+    from muzero_b200.distributed import kv_split_decode_attention, kv_split_ranges
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    lo, hi = kv_split_ranges(args.context, world, args.group)[rank]
+    res = RES if rank == world - 1 else 0
+    import muzero_b200 as mz
+    gen = torch.Generator(device=device).manual_seed(77)            # same stream on every rank: identical q
+    q = torch.randn(args.batch, QH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+    gen.manual_seed(1000 + rank)
+    layers = []
+    for _ in range(args.layers):
+        layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=args.bits, q_group_size=args.group, residual_length=res,
+                                                    alpha_key=2.0, alpha_value=2.0))
+        n = hi - lo + res
+        k = torch.randn(args.batch, KVH, n, D, device=device, generator=gen).to(torch.bfloat16)
+        v = torch.randn(args.batch, KVH, n, D, device=device, generator=gen).to(torch.bfloat16)
+        layer.update(k, v, {"materialize_full_kv": False})
+        del k, v
+        layers.append(layer)
+
+    def one_round():
+        for layer in layers:
+            if world > 1:
+                kv_split_decode_attention(layer, q, D ** -0.5)
+            else:
+                from muzero_b200.cache.attention import decode_attention
+                decode_attention(layer, q, D ** -0.5)
+
+    for _ in range(args.warmup):
+        one_round()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        one_round()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    us = ms.item() * 1e3 / (args.steps * len(layers))
+    abytes = algorithmic_bytes(args.bits, batch=args.batch, sq=args.context, group=args.group)
+    peak, kind = measured_peak_gbs()
+    return {"mode": "kv-split", "n_gpus": world, "bits": args.bits, "group": args.group, "batch": args.batch,
+            "context": args.context, "layers": args.layers, "us_per_call": us, "bytes_per_call_all_ranks": abytes,
+            "achieved_gbs_all_ranks": abytes / us / 1e3, "frac_of_peak_per_gpu": abytes / us / 1e3 / peak / world,
+            "peak_kind": kind} if rank == 0 else {}
+
+
 def run_generate(args) -> dict:
     """BASELINE config 2 (secondary workload): greedy `generate()` on a random-init (std 0.02)
     Qwen3-8B-architecture decoder in bf16 through `patch_transformers()` and
@@ -430,6 +493,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--attention-only", action="store_true", help="small profiling case: only the fused attention calls")
+    ap.add_argument("--kv-split", action="store_true", help="secondary workload: one long context split over the GPUs of the run")
     ap.add_argument("--generate", action="store_true", help="secondary workload: HF generate() on a Qwen3-8B shaped model")
     ap.add_argument("--cache", default="mu_zero", choices=["mu_zero", "dynamic"])
     ap.add_argument("--context", type=int, default=CTX, help="quantized tokens per sequence (--attention-only, --generate)")
@@ -442,6 +506,11 @@ def main():
         return
     if args.attention_only:
         print(json.dumps(run_attention_only(args)))
+        return
+    if args.kv_split:
+        out = run_kv_split(args)
+        if out:
+            print(json.dumps(out))
         return
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out:
