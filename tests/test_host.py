@@ -44,6 +44,14 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.mz_flush_kv(ctypes.byref(s), 64, 1e-8, None) == 1
     a = _cabi.DecodeArgs()
     assert lib.mz_decode_workspace_bytes(ctypes.byref(a)) == 0
+    # the fused step validates before it launches anything, too
+    assert lib.mz_decode_step_workspace_bytes(ctypes.byref(a), 128, 64) == 0
+    assert lib.mz_decode_step(None, None, None, 0, 0, 128, 64, 0, 0, 1e-8, None) == 1
+    a.store.group = 64
+    assert lib.mz_decode_step(ctypes.byref(a), None, None, 0, 0, 128, 96, 0, 0, 1e-8, None) == 1
+    assert "flush_unit" in _cabi.last_error()
+    assert lib.mz_decode_step(ctypes.byref(a), None, None, 0, 0, 128, 64, 0, 0, 1e-8, None) == 4     # window has no room
+    assert "window" in _cabi.last_error()
 
 
 def test_cpu_tensors_are_rejected_not_silently_handled():
