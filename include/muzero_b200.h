@@ -115,6 +115,16 @@ typedef struct mz_kv_store {
 int mz_flush_kv(const mz_kv_store* store, int n_tokens, float eps, void* stream);
 
 /*
+ * The same flush with separate extents for keys and values: the n_key_tokens oldest residual tokens
+ * (a multiple of group) go to key group k_groups.., the residual rows [value_first, value_first +
+ * n_value_tokens) go to value tokens v_tokens...  For the reference's `logq_compatible_layout`, where
+ * every value token beyond the residual length is flushed while keys flush by whole groups, so the
+ * value prefix runs ahead of the key prefix (muzero/cache/layer.py:389-396).
+ */
+int mz_flush_kv_parts(const mz_kv_store* store, int n_key_tokens, int value_first, int n_value_tokens, float eps,
+                      void* stream);
+
+/*
  * Appends one token per (b,kvh) to the residual window at index res_start+res_len:
  * k_new,v_new [B,KVH,1,D] with element strides (new_stride_b,new_stride_h).
  * Replaces: the two single-token buffer copies of _append_dense, muzero/cache/layer.py:183-193.

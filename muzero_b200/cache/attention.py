@@ -97,12 +97,61 @@ def decode_attention(layer, query: torch.Tensor, scaling: float, attention_mask:
                      *, out_dtype: Optional[torch.dtype] = None, splits: int = 0) -> torch.Tensor:
     """[B,H,1,D] query -> [B,1,H,D] attention output over ``layer``'s prefix + residual."""
     b, h, _, d = query.shape
+    if layer._key_group_count * layer.q_group_size != layer._value_storage_len:
+        return _decode_attention_unaligned(layer, query, scaling, attention_mask, out_dtype or query.dtype)
     out = torch.empty((b, 1, h, d), dtype=out_dtype or query.dtype, device=query.device)
     args = build_decode_args(layer, query, scaling, attention_mask, out, splits=splits)
     with torch.cuda.device(query.device):
         check(load_mu_zero_cuda_extension().mz_decode_attention(ctypes.byref(args), stream_ptr(query.device)),
               "mz_decode_attention")
     return out
+
+
+def _decode_attention_unaligned(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor],
+                                out_dtype: torch.dtype) -> torch.Tensor:
+    """Decode attention when the value prefix is ahead of the key prefix (``logq_compatible_layout``).
+
+    The fused kernel pairs key and value tiles of the same tokens, which this legacy layout does not
+    offer; this route is the reference's own structure (muzero/cache/attention.py:104-151,186-263) in
+    fp32: packed keys through ``mz_qk_logits``, packed values through ``mz_av_output``, the two dense
+    residual pieces and the softmax in torch.  It is the slow path of a compatibility flag."""
+    from ..kernels.loader import ensure_expand_table
+    if not query.is_cuda:
+        raise MuZeroKernelError("decode attention needs CUDA tensors; this package has no CPU path")
+    b, h, _, d = query.shape
+    dev, g = query.device, layer.q_group_size
+    kvh = layer.keys.shape[1]
+    gqa = h // kvh
+    p_k, p_v = layer._key_group_count * g, layer._value_storage_len
+    lib, st, f32 = load_mu_zero_cuda_extension(), stream_ptr(dev), dtype_code(torch.float32)
+    q = query if query.stride(-1) == 1 else query.contiguous()
+    store = layer._store_struct()
+    qg = q.float().reshape(b, kvh, gqa, d)
+    pieces = []
+    with torch.cuda.device(dev):
+        if p_k:
+            ensure_expand_table(layer.nbits, layer._selected_alpha_key, dev)
+            lg = torch.empty((b, h, p_k), dtype=torch.float32, device=dev)
+            check(lib.mz_qk_logits(ctypes.byref(store), q.data_ptr(), q.stride(0), q.stride(1), h, float(scaling),
+                                   lg.data_ptr(), f32, st), "mz_qk_logits")
+            pieces.append(lg)
+        if layer.keys.shape[2]:
+            pieces.append((torch.matmul(qg, layer.keys.float().transpose(-1, -2)) * scaling).reshape(b, h, -1))
+        logits = torch.cat(pieces, dim=-1)
+        if attention_mask is not None:
+            mask = attention_mask.to(torch.float32)
+            if mask.dim() != 4 or mask.shape[-1] < logits.shape[-1]:
+                raise MuZeroKernelError(f"attention_mask must be [B,1,1,>={logits.shape[-1]}], got {tuple(mask.shape)}")
+            logits = logits + mask[:, 0, :, : logits.shape[-1]]
+        w = torch.softmax(logits, dim=-1)
+        out = torch.zeros((b, h, d), dtype=torch.float32, device=dev)
+        if p_v:
+            ensure_expand_table(layer.nbits, layer._selected_alpha_value, dev)
+            wp = w[..., :p_v].contiguous()
+            check(lib.mz_av_output(ctypes.byref(store), wp.data_ptr(), f32, p_v, h, out.data_ptr(), f32, st), "mz_av_output")
+        if layer.values.shape[2]:
+            out = out + torch.matmul(w[..., p_v:].reshape(b, kvh, gqa, -1), layer.values.float()).reshape(b, h, d)
+    return out.reshape(b, 1, h, d).to(out_dtype)
 
 
 def decode_attention_partial(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor] = None,

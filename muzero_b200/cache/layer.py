@@ -65,6 +65,9 @@ class MuZeroCacheLayer:
         self._value_buffer = None
         self._buffer_capacity = 0
         self._res_start = 0
+        # logq_compatible_layout: tokens by which the value prefix is ahead of the key prefix.  The window
+        # rows [0, _value_lead) then still hold keys only; `values` is the window without them.
+        self._value_lead = 0
         for name in _STORE_ATTRS:
             setattr(self, name, None)
         self._bufs: dict[str, torch.Tensor] = {}
@@ -132,6 +135,7 @@ class MuZeroCacheLayer:
     def _rehome_residual(self, min_tokens: int) -> None:
         """Puts the residual window at the front of a buffer with room for ``min_tokens``."""
         cur = int(self.keys.shape[2]) if self.keys.numel() else 0
+        lead = self._value_lead
         if self._key_buffer is None or self._buffer_capacity < min_tokens:
             cap = residual_capacity(min_tokens, self.residual_length, self.q_group_size)
             shape_k = (*self.keys.shape[:2], cap, self.k_head_dim)
@@ -140,17 +144,17 @@ class MuZeroCacheLayer:
             vb = torch.empty(shape_v, dtype=self.dtype, device=self.device)
             if cur:
                 kb[:, :, :cur].copy_(self.keys)
-                vb[:, :, :cur].copy_(self.values)
+                vb[:, :, lead:cur].copy_(self.values)
             self._key_buffer, self._value_buffer, self._buffer_capacity = kb, vb, cap
         elif self._res_start > 0 and cur:
             src_k, src_v = self.keys, self.values
             if self._res_start < cur:          # overlapping move
                 src_k, src_v = src_k.clone(), src_v.clone()
             self._key_buffer[:, :, :cur].copy_(src_k)
-            self._value_buffer[:, :, :cur].copy_(src_v)
+            self._value_buffer[:, :, lead:cur].copy_(src_v)
         self._res_start = 0
         self.keys = self._key_buffer[:, :, :cur]
-        self.values = self._value_buffer[:, :, :cur]
+        self.values = self._value_buffer[:, :, lead:cur]
 
     def _append_dense(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
         n_new = int(key_states.shape[2])
@@ -175,27 +179,34 @@ class MuZeroCacheLayer:
                 self._value_buffer[:, :, pos:pos + 1].copy_(value_states)
             a = self._res_start
             self.keys = self._key_buffer[:, :, a:a + cur + 1]
-            self.values = self._value_buffer[:, :, a:a + cur + 1]
+            self.values = self._value_buffer[:, :, a + self._value_lead:a + cur + 1]
             return
         self.keys = torch.cat([self.keys, key_states], dim=-2)
         self.values = torch.cat([self.values, value_states], dim=-2)
         self._key_buffer = self._value_buffer = None
         self._buffer_capacity = 0
         self._res_start = 0
+        if self._value_lead:                   # keep keys and values addressable as one window
+            self._rehome_residual(int(self.keys.shape[2]) + 1)
 
-    def _drop_residual_prefix(self, n: int) -> None:
-        """Forgets the ``n`` oldest residual tokens (they are in the store now)."""
-        if n <= 0:
+    def _drop_residual_prefix(self, n: int, n_values: Optional[int] = None) -> None:
+        """Forgets the ``n`` oldest residual keys and ``n_values`` (default ``n``) oldest residual values
+        (they are in the store now)."""
+        n_values = n if n_values is None else n_values
+        if n <= 0 and n_values <= 0:
             return
+        lead = self._value_lead + n_values - n
         if self._key_buffer is not None:
             self._res_start += n
+            self._value_lead = lead
             a, cur = self._res_start, int(self.keys.shape[2]) - n
             self.keys = self._key_buffer[:, :, a:a + cur]
-            self.values = self._value_buffer[:, :, a:a + cur]
+            self.values = self._value_buffer[:, :, a + lead:a + cur]
         else:
             # aliased prefill block: keep only the tail, in a buffer of its own
             self.keys = self.keys[:, :, n:]
-            self.values = self.values[:, :, n:]
+            self.values = self.values[:, :, n_values:]
+            self._value_lead = lead
             self._rehome_residual(int(self.keys.shape[2]) + 1)
 
     # ----------------------------------------------------------------- store
@@ -247,13 +258,14 @@ class MuZeroCacheLayer:
         self._refresh_views()
 
     # ------------------------------------------------------------------ alpha
-    def _ensure_alpha(self, n_flush: int) -> None:
+    def _ensure_alpha(self, n_flush: int, n_values: Optional[int] = None) -> None:
+        n_values = n_flush if n_values is None else n_values
         g, bits, mp = self.q_group_size, self.nbits, self.cfg.stats_max_points
-        if self._selected_alpha_key is None:
+        if self._selected_alpha_key is None and n_flush > 0:
             self._selected_alpha_key = select_alpha_key_block(self.keys[:, :, :n_flush], bits=bits, q_group_size=g,
                                                               max_points=mp)
-        if self._selected_alpha_value is None:
-            self._selected_alpha_value = _select_alpha_value_block(self.values[:, :, :n_flush], bits=bits, group=g,
+        if self._selected_alpha_value is None and n_values > 0:
+            self._selected_alpha_value = _select_alpha_value_block(self.values[:, :, :n_values], bits=bits, group=g,
                                                                    d_pad=self.v_head_dim_padded, max_points=mp)
 
     # ------------------------------------------------------------------ flush
@@ -264,23 +276,24 @@ class MuZeroCacheLayer:
         plan = plan_flush(key_len=int(self.keys.shape[2]), value_len=int(self.values.shape[2]),
                           residual_length=self.residual_length, group=self.q_group_size, decode_flush=decode_flush,
                           flush_by_group=self.cfg.decode_flush_by_group, logq_layout=self.cfg.logq_compatible_layout)
-        if self.cfg.logq_compatible_layout and plan.value_tokens != plan.key_tokens:
-            raise NotImplementedError("logq_compatible_layout with unequal key/value prefixes is not supported yet")
-        n = plan.key_tokens
-        if n == 0:
+        n, nv = plan.key_tokens, plan.value_tokens
+        if n == 0 and nv == 0:
             return
         self._require_device_path()
-        self._ensure_alpha(n)
+        self._ensure_alpha(n, nv)
         g = self.q_group_size
-        self._ensure_store(self._key_group_count + n // g, self._value_storage_len + n)
+        self._ensure_store(self._key_group_count + n // g, self._value_storage_len + nv)
+        if self._value_lead and self._key_buffer is None:
+            self._rehome_residual(int(self.keys.shape[2]) + 1)      # one window for keys and values
         s = self._store_struct()
         with torch.cuda.device(self.device):
-            check(load_mu_zero_cuda_extension().mz_flush_kv(ctypes.byref(s), n, self.amax_eps, stream_ptr(self.device)),
-                  "mz_flush_kv")
+            # value rows are addressed inside the key window: they start `_value_lead` rows in
+            check(load_mu_zero_cuda_extension().mz_flush_kv_parts(ctypes.byref(s), n, self._value_lead, nv, self.amax_eps,
+                                                                  stream_ptr(self.device)), "mz_flush_kv_parts")
         self._key_group_count += n // g
-        self._value_storage_len += n
+        self._value_storage_len += nv
         self._refresh_views()
-        self._drop_residual_prefix(n)
+        self._drop_residual_prefix(n, nv)
 
     # ---------------------------------------------------------------- dequant
     def _dequantize(self, g0: int, g1: int, t0: int, t1: int, want_k: bool, want_v: bool):
@@ -333,10 +346,9 @@ class MuZeroCacheLayer:
             self.compress_residual_prefix(decode_flush=key_states.shape[-2] == 1)
         if first:
             return raw_k, raw_v
-        if not materialize or self._key_group_count == 0:
+        if not materialize:
             return self.keys, self.values
-        return (torch.cat([self._dequantize_key_prefix(), self.keys], dim=2),
-                torch.cat([self._dequantize_value_prefix(), self.values], dim=2))
+        return self._full_kv()
 
     def decode_step(self, key_states: torch.Tensor, value_states: torch.Tensor, query: torch.Tensor, scaling: float,
                     attention_mask: torch.Tensor | None = None) -> torch.Tensor:
@@ -408,10 +420,9 @@ class MuZeroCacheLayer:
 
     # ------------------------------------------------------ cache management
     def _full_kv(self) -> tuple[torch.Tensor, torch.Tensor]:
-        if self._key_group_count == 0:
-            return self.keys, self.values
-        return (torch.cat([self._dequantize_key_prefix(), self.keys], dim=2),
-                torch.cat([self._dequantize_value_prefix(), self.values], dim=2))
+        k = torch.cat([self._dequantize_key_prefix(), self.keys], dim=2) if self._key_group_count else self.keys
+        v = torch.cat([self._dequantize_value_prefix(), self.values], dim=2) if self._value_storage_len else self.values
+        return k, v
 
     def crop(self, max_length: int) -> None:
         if max_length < 0:

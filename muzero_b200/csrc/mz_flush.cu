@@ -13,13 +13,14 @@ namespace {
 
 struct FlushParams {
   mz_kv_store s;
-  int n_tokens, n_tiles;     // tokens to flush, = n_tiles * G
+  int n_tiles;               // key tiles (groups of G tokens) to flush, from the window's first token
+  int v_first, n_vtokens;    // value tokens to flush: window rows [v_first, v_first + n_vtokens)
   int QB, NG;
   float eps;
   const uint16_t* ctab_k; int ctab_k_n;
   const uint16_t* ctab_v; int ctab_v_n;
   unsigned n_k_blocks;
-  long long v_rows;          // B*KVH*n_tokens*NG
+  long long v_rows;          // B*KVH*n_vtokens*NG
   int v_fast;                // G/8 lanes per value row, D % 8 == 0
   int k_vec;                 // key tile rows can be loaded as 16-byte vectors
 };
@@ -84,7 +85,7 @@ __device__ void flush_value_rows_fast(const FlushParams& p) {
   const bool live = row < p.v_rows;
   long long r = live ? row : 0;
   const int grp = (int)(r % p.NG); r /= p.NG;
-  const int t = (int)(r % p.n_tokens); r /= p.n_tokens;
+  const int t = (int)(r % p.n_vtokens); r /= p.n_vtokens;
   const int h = (int)(r % s.kv_heads);
   const int b = (int)(r / s.kv_heads);
   const int c0 = grp * G + sub * 8;
@@ -93,7 +94,7 @@ __device__ void flush_value_rows_fast(const FlushParams& p) {
   for (int i = 0; i < 8; ++i) v[i] = 0.f;
   if (live && c0 < D) {
     const uint16_t* src = (const uint16_t*)s.res_v + b * s.res_stride_b + h * s.res_stride_h +
-                          (long long)(s.res_start + t) * s.res_stride_t + c0;
+                          (long long)(s.res_start + p.v_first + t) * s.res_stride_t + c0;
     if (p.k_vec) {
       const uint4 raw = *(const uint4*)src;
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -140,11 +141,11 @@ __device__ void flush_value_rows_generic(const FlushParams& p) {
   if (row >= p.v_rows) return;
   long long r = row;
   const int grp = (int)(r % p.NG); r /= p.NG;
-  const int t = (int)(r % p.n_tokens); r /= p.n_tokens;
+  const int t = (int)(r % p.n_vtokens); r /= p.n_vtokens;
   const int h = (int)(r % s.kv_heads);
   const int b = (int)(r / s.kv_heads);
   const uint16_t* src = (const uint16_t*)s.res_v + b * s.res_stride_b + h * s.res_stride_h +
-                        (long long)(s.res_start + t) * s.res_stride_t;
+                        (long long)(s.res_start + p.v_first + t) * s.res_stride_t;
   float mn = INFINITY, mx = -INFINITY;
   for (int i = lane; i < G; i += 32) {
     const int c = grp * G + i;
@@ -251,21 +252,26 @@ __global__ void __launch_bounds__(256) dequant_values_kernel(const mz_kv_store s
 bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 }  // namespace
 
-extern "C" int mz_flush_kv(const mz_kv_store* s, int n_tokens, float eps, void* stream) {
+extern "C" int mz_flush_kv_parts(const mz_kv_store* s, int n_key_tokens, int value_first, int n_value_tokens, float eps,
+                                 void* stream) {
   int rc = mz_check_store_basic(s);
   if (rc) return rc;
   if ((rc = mz_check_store_quantized(s))) return rc;
   if ((rc = mz_check_store_residual(s))) return rc;
-  MZ_REQUIRE(n_tokens >= 0 && n_tokens % s->group == 0, "n_tokens %d is not a multiple of group %d", n_tokens, s->group);
-  MZ_REQUIRE(n_tokens <= s->res_len, "flush of %d tokens but residual holds %d", n_tokens, s->res_len);
-  if (n_tokens == 0) return MZ_OK;
+  MZ_REQUIRE(n_key_tokens >= 0 && n_key_tokens % s->group == 0, "n_key_tokens %d is not a multiple of group %d", n_key_tokens,
+             s->group);
+  MZ_REQUIRE(n_key_tokens <= s->res_len, "flush of %d key tokens but residual holds %d", n_key_tokens, s->res_len);
+  MZ_REQUIRE(value_first >= 0 && n_value_tokens >= 0 && value_first + n_value_tokens <= s->res_len,
+             "value tokens [%d, %d) outside the residual window of %d", value_first, value_first + n_value_tokens, s->res_len);
+  if (n_key_tokens == 0 && n_value_tokens == 0) return MZ_OK;
   const MzStoreGeom g = mz_geom(*s);
   FlushParams p;
-  p.s = *s; p.n_tokens = n_tokens; p.n_tiles = n_tokens / g.G; p.QB = g.QB; p.NG = g.NG; p.eps = eps;
+  p.s = *s; p.n_tiles = n_key_tokens / g.G; p.v_first = value_first; p.n_vtokens = n_value_tokens;
+  p.QB = g.QB; p.NG = g.NG; p.eps = eps;
   if ((rc = mz_get_compand_table(g.kv_dt, s->alpha_key, &p.ctab_k, &p.ctab_k_n))) return rc;
   if ((rc = mz_get_compand_table(g.kv_dt, s->alpha_value, &p.ctab_v, &p.ctab_v_n))) return rc;
   const long long kb = (long long)g.B * g.KVH * p.n_tiles;
-  p.v_rows = (long long)g.B * g.KVH * n_tokens * g.NG;
+  p.v_rows = (long long)g.B * g.KVH * n_value_tokens * g.NG;
   p.v_fast = pow2(g.G) && g.G >= 8 && g.G <= 256 && g.D % 8 == 0;
   p.k_vec = g.D % 8 == 0 && s->res_stride_t % 8 == 0 && s->res_stride_h % 8 == 0 && s->res_stride_b % 8 == 0 &&
             (uintptr_t)s->res_k % 16 == 0 && (uintptr_t)s->res_v % 16 == 0;
@@ -285,6 +291,10 @@ extern "C" int mz_flush_kv(const mz_kv_store* s, int n_tokens, float eps, void* 
   }
   MZ_LAUNCH_CHECK("flush_kv");
   return MZ_OK;
+}
+
+extern "C" int mz_flush_kv(const mz_kv_store* s, int n_tokens, float eps, void* stream) {
+  return mz_flush_kv_parts(s, n_tokens, 0, n_tokens, eps, stream);
 }
 
 extern "C" int mz_append_kv(const mz_kv_store* s, const void* k_new, const void* v_new, long long nsb, long long nsh, void* stream) {

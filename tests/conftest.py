@@ -53,6 +53,8 @@ def golden():
         tables = np.load(os.path.join(GOLDEN, "expand_tables.npz"))
         layer = np.load(os.path.join(GOLDEN, "layer_cases.npz"))
         layer_meta = json.load(open(os.path.join(GOLDEN, "layer_cases.json")))
+        layer_logq = np.load(os.path.join(GOLDEN, "layer_cases_logq.npz"))
+        layer_logq_meta = json.load(open(os.path.join(GOLDEN, "layer_cases_logq.json")))
         config0 = np.load(os.path.join(GOLDEN, "config0.npz"))
         config0_meta = json.load(open(os.path.join(GOLDEN, "config0.json")))
         alpha = json.load(open(os.path.join(GOLDEN, "alpha_cases.json")))

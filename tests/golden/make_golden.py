@@ -12,6 +12,7 @@ Outputs (all small, committed):
   expand_tables.npz   expm1 compander tables (bits<=6 in full, sha256 for 7/8)
   layer_cases.npz     MuZeroCacheLayer states (prefill flush, per-token decode
                       flush) and decode-attention outputs (as-is and fp32 evaluation)
+  layer_cases_logq.npz  the same for ``logq_compatible_layout=True`` (``--only logq`` writes just these)
   config0.npz         BASELINE config 0 at full size: sha256 of every store
                       tensor + the attention outputs
   alpha_cases.json    ``select_alpha`` results on the synthetic distributions
@@ -73,6 +74,7 @@ def row_inputs(n_rows: int, group: int, seed: int) -> torch.Tensor:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default="all", choices=["all", "logq"], help="logq: write just layer_cases_logq.*")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import muzero  # the reference
@@ -116,8 +118,9 @@ def main():
                             outbf = _dequantize_rows_torch(pq, mn, sc, bits, alpha, group, torch.bfloat16, 1e-8)
                             deq[key + "_f32"] = out32.numpy()
                             deq[key + "_bf16"] = bits16(outbf)
-    np.savez_compressed(os.path.join(HERE, "rows_quant.npz"), **quant)
-    np.savez_compressed(os.path.join(HERE, "rows_dequant.npz"), **deq)
+    if args.only == "all":
+        np.savez_compressed(os.path.join(HERE, "rows_quant.npz"), **quant)
+        np.savez_compressed(os.path.join(HERE, "rows_dequant.npz"), **deq)
 
     # ---------------------------------------------------------------- tables
     tabs = {}
@@ -132,7 +135,8 @@ def main():
                 tabs[f"b{bits}_a{int(alpha)}"] = t.numpy()
             else:
                 tabs[f"b{bits}_a{int(alpha)}_sha"] = np.frombuffer(bytes.fromhex(sha(t)), dtype=np.uint8)
-    np.savez_compressed(os.path.join(HERE, "expand_tables.npz"), **tabs)
+    if args.only == "all":
+        np.savez_compressed(os.path.join(HERE, "expand_tables.npz"), **tabs)
 
     # ----------------------------------------------------------- layer cases
     def ref_layer(bits, group, residual, **kw):
@@ -179,6 +183,17 @@ def main():
         ("c4g64_bf16meta", 4, 64, 128, 1, 2, 8, 256, 128, 0, {"amax_dtype": "bfloat16"}),
         ("c4g64_f32meta", 4, 64, 128, 1, 2, 8, 256, 128, 0, {"amax_dtype": "float32"}),
     ]
+    logq_specs = [
+        # the legacy layout: every value token beyond the residual length is flushed, keys flush by whole groups,
+        # so the value prefix runs ahead of the key prefix by up to group-1 tokens
+        ("c4g64_logq", 4, 64, 128, 1, 2, 8, 300, 128, 0, {"logq_compatible_layout": True}),
+        ("c4g64_logq_dec", 4, 64, 128, 2, 2, 8, 200, 128, 90, {"logq_compatible_layout": True}),
+        ("c2g32_logq_dec", 2, 32, 64, 1, 2, 4, 150, 128, 40, {"logq_compatible_layout": True}),
+    ]
+    if args.only == "logq":
+        specs, stem = logq_specs, "layer_cases_logq"
+    else:
+        stem = "layer_cases"
     for (name, bits, group, residual, B, KVH, H, S, D, steps, extra) in specs:
         seed = abs(hash(name)) % 100000 if False else sum(ord(c) for c in name)
         k, v, q = orc.synth_kv(B, KVH, S + steps, D, H, seed=seed)
@@ -195,9 +210,12 @@ def main():
         meta[name] = dict(bits=bits, group=group, residual=residual, B=B, KVH=KVH, H=H, S=S, D=D,
                           steps=steps, seed=seed, extra=extra,
                           input_sha=dict(k=sha(k), v=sha(v), q=sha(q)), deq_bf16_sha=deq_sha)
-    np.savez_compressed(os.path.join(HERE, "layer_cases.npz"), **cases)
-    with open(os.path.join(HERE, "layer_cases.json"), "w") as f:
+    np.savez_compressed(os.path.join(HERE, stem + ".npz"), **cases)
+    with open(os.path.join(HERE, stem + ".json"), "w") as f:
         json.dump(meta, f, indent=1, sort_keys=True)
+    if args.only == "logq":
+        print("wrote", stem)
+        return
 
     # --------------------------------------------------------------- config 0
     cfg0 = {}

@@ -200,3 +200,29 @@ def test_decode_step_with_mask_and_refusals(oracle):
     assert torch.equal(got, want)
     with pytest.raises(MuZeroKernelError):
         b.decode_step(k[:, :, 400:401], v[:, :, 400:401], q, 0.09, mask)      # 402 tokens now, mask has 401
+
+
+@pytest.mark.parametrize("hf_strides", [False, True])
+@pytest.mark.parametrize("name", ["c4g64_logq", "c4g64_logq_dec", "c2g32_logq_dec"])
+def test_logq_layout_matches_reference(oracle, golden, name, hf_strides):
+    """`logq_compatible_layout=True`: keys flush by whole groups, values token by token, so the value
+    prefix runs ahead; store, residual windows and attention against the reference's own run."""
+    from muzero_b200.cache.attention import decode_attention
+    meta, g = golden.layer_logq_meta[name], golden.layer_logq
+    layer, q = gpu_layer_from_meta(oracle, meta, hf_strides)
+    assert np.array_equal(layer._packed_key_q.cpu().numpy(), g[name + "/packed_k"])
+    assert np.array_equal(layer._packed_value_q.cpu().numpy(), g[name + "/packed_v"])
+    for attr, nm in (("_key_mn", "k_mn"), ("_key_scale", "k_scale"), ("_value_mn", "v_mn"), ("_value_scale", "v_scale")):
+        assert np.array_equal(_meta_arr(getattr(layer, attr)), g[f"{name}/{nm}"]), nm
+    assert np.array_equal(bits16(layer.keys), g[name + "/res_k"])
+    assert np.array_equal(bits16(layer.values), g[name + "/res_v"])
+    assert [layer._selected_alpha_key, layer._selected_alpha_value] == list(g[name + "/alpha"])
+    assert sha(layer._dequantize_key_prefix()) == meta["deq_bf16_sha"]["k"]
+    assert sha(layer._dequantize_value_prefix()) == meta["deq_bf16_sha"]["v"]
+    state = layer.get_attention_state()
+    assert state["value_prefix_length"] > state["key_prefix_length"] > 0
+    ref = torch.from_numpy(g[name + "/attn_fp32"])
+    out = decode_attention(layer, q, meta["D"] ** -0.5, out_dtype=torch.float32)
+    assert (out.cpu() - ref).abs().max().item() <= 2e-3
+    k_full, v_full = layer._full_kv()
+    assert k_full.shape == v_full.shape and k_full.shape[2] == meta["S"] + meta["steps"]

@@ -93,7 +93,8 @@ def build_case(oracle, meta):
     assert sha(k) == meta["input_sha"]["k"] and sha(v) == meta["input_sha"]["v"] and sha(q) == meta["input_sha"]["q"]
     layer = oracle.OracleCacheLayer(bits=meta["bits"], group=meta["group"], residual=meta["residual"],
                                     meta_dtype=md[extra.get("amax_dtype", "float16")],
-                                    flush_by_group=extra.get("decode_flush_by_group", True))
+                                    flush_by_group=extra.get("decode_flush_by_group", True),
+                                    logq_layout=extra.get("logq_compatible_layout", False))
     S = meta["S"]
     layer.append(k[:, :, :S].contiguous(), v[:, :, :S].contiguous())
     for i in range(meta["steps"]):
@@ -104,9 +105,19 @@ def build_case(oracle, meta):
 @pytest.mark.parametrize("name", ["c4g64", "c2g64", "c3g32", "c8g128", "c1g64", "c7g64", "c4g64_d64",
                                   "c4g64_dec", "c2g64_dec4g", "c4g64_bf16meta", "c4g64_f32meta"])
 def test_layer_cases_match_reference(oracle, golden, name):
-    meta = golden.layer_meta[name]
+    _check_layer_case(oracle, golden.layer_meta[name], golden.layer, name)
+
+
+@pytest.mark.parametrize("name", ["c4g64_logq", "c4g64_logq_dec", "c2g32_logq_dec"])
+def test_logq_layout_cases_match_reference(oracle, golden, name):
+    """`logq_compatible_layout=True`: the value prefix runs ahead of the key prefix."""
+    g = golden.layer_logq
+    assert g[name + "/packed_v"].shape[2] > g[name + "/packed_k"].shape[2] * golden.layer_logq_meta[name]["group"]
+    _check_layer_case(oracle, golden.layer_logq_meta[name], g, name)
+
+
+def _check_layer_case(oracle, meta, g, name):
     layer, q = build_case(oracle, meta)
-    g = golden.layer
     assert np.array_equal(layer.packed_k.numpy(), g[name + "/packed_k"])
     assert np.array_equal(layer.packed_v.numpy(), g[name + "/packed_v"])
     for nm in ("k_mn", "k_scale", "v_mn", "v_scale"):
