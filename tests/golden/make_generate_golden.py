@@ -40,7 +40,8 @@ def prompt_ids(recipe):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MUZERO_REFERENCE"), required="MUZERO_REFERENCE" not in os.environ,
+                    help="path of the reference checkout (or set MUZERO_REFERENCE)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import muzero

@@ -3,7 +3,7 @@
 Run where the reference checkout is available (it is imported read-only and
 run on CPU through its own ``backend="torch"`` path):
 
-    python tests/golden/make_golden.py [--reference /path/to/reference]
+    python tests/golden/make_golden.py --reference /path/to/reference
 
 Outputs (all small, committed):
   rows_quant.npz      seeded row inputs + packed codes / mn / scale of
@@ -73,7 +73,8 @@ def row_inputs(n_rows: int, group: int, seed: int) -> torch.Tensor:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MUZERO_REFERENCE"), required="MUZERO_REFERENCE" not in os.environ,
+                    help="path of the reference checkout (or set MUZERO_REFERENCE)")
     ap.add_argument("--only", default="all", choices=["all", "logq"], help="logq: write just layer_cases_logq.*")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
