@@ -12,6 +12,7 @@ template <int DT>
 struct MzQuantRow {
   float lo, span, anchor, zero_code, steps_up, steps_dn, room_up, room_dn;
   float inv_span, inv_up, inv_dn;   // correctly rounded reciprocals of the three per-row divisors
+  bool row_nan;                     // the zero anchor is NaN (0/0 range): every code of the row is 0
   float alpha, log_base, top;
   const uint16_t* __restrict__ ctab;
   int ctab_n;
@@ -38,6 +39,7 @@ struct MzQuantRow {
     inv_span = __frcp_rn(span);
     inv_up = __frcp_rn(room_up);
     inv_dn = __frcp_rn(room_dn);
+    row_nan = anchor != anchor;
   }
 
   // round_T(num / den) for a per-row divisor `den` with inv = RN(1/den).  bf16: num*inv is within 1.5
@@ -71,7 +73,7 @@ struct MzQuantRow {
     // NaN (0/0 when the row range or a side extent rounds to zero in T) propagates through the
     // reference's chain and its final cast to uint8 yields 0; mirror that outcome.
     float unit = quotient(TT::round(__fsub_rn(x, lo)), span, inv_span);
-    if (unit != unit || anchor != anchor) return 0;
+    if (unit != unit || row_nan) return 0;
     unit = fminf(fmaxf(unit, 0.0f), 1.0f);
     // one path for both sides of the zero anchor (lanes of a warp straddle it): round(a-b) == -round(b-a)
     const bool up = unit >= anchor;
@@ -79,10 +81,13 @@ struct MzQuantRow {
     float p = quotient(num, up ? room_up : room_dn, up ? inv_up : inv_dn);
     if (p != p) return 0;
     p = fminf(fmaxf(p, 0.0f), 1.0f);
-    const float rr = rintf(TT::round(__fmul_rn(compand(p), up ? steps_up : steps_dn)));
-    float q = TT::round(up ? __fadd_rn(zero_code, rr) : __fsub_rn(zero_code, rr));
+    // round-half-even of a value in [0, 255] by adding and removing 1.5 * 2^23 (keeps the conversion pipe free)
+    constexpr float kMagic = 12582912.0f;
+    const float rr = __fsub_rn(__fadd_rn(TT::round(__fmul_rn(compand(p), up ? steps_up : steps_dn)), kMagic), kMagic);
+    // zero_code +- rr: integers; where rounding to T would change them (beyond 256) the clamp below decides anyway
+    float q = up ? __fadd_rn(zero_code, rr) : __fsub_rn(zero_code, rr);
     q = fminf(fmaxf(q, 0.0f), top);
-    return (int)q;
+    return __float_as_int(__fadd_rn(q, kMagic)) & 0x1ff;
   }
 };
 
