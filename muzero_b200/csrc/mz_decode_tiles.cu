@@ -520,85 +520,64 @@ __global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_t
 }
 
 // ---- merge of the records of one (batch, kv head) pair: one CTA per pair, one warp-quad (128
-// threads) per query head.  Thread 0 lists the record slots of the warps whose tile ranges meet
-// this pair (from the same partition formula the main kernel uses); everyone then merges them.
-constexpr int kMaxCombineSlots = 64;
+// threads) per query head.  The warps of the main kernel that hold records of the pair are found from
+// the partition functions the main kernel uses: warp g owns the tiles whose start cost lies in
+// [cost(g), cost(g+1)), and cost(g) is within [g*quot, g*(quot+1)), so every contributor lies in the
+// candidate range [c_lo/(quot+1) - 1, (c_hi-1)/quot + 1], c_lo..c_hi being the pair's cost interval.
+// All threads test candidates at once; the list keeps the candidates' order (a fixed merge order).
+// WIDE (many records per pair, few pairs): one CTA per (pair, head); its four warp-quads each merge every
+// fourth chunk of records and the four partial states are merged in a fixed order at the end.
+constexpr int kMaxCombineSlots = 4096;
+template <bool WIDE>
 __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
-  __shared__ long long s_slot[kMaxCombineSlots];
-  __shared__ int s_n;
-  __shared__ long long s_first;
-  const int pair = blockIdx.x;
+  __shared__ int s_slot[kMaxCombineSlots];     // record slot of candidate i, or -1
+  __shared__ float s_part[WIDE ? 4 : 1][WIDE ? 130 : 1];
+  const int pair = WIDE ? blockIdx.x / p.gqa : blockIdx.x;
   const int W = p.tp.total_warps, T = p.tp.tiles_per_pair, gqa = p.gqa;
   const long long lo = (long long)pair * T, hi = lo + T;
-  if (threadIdx.x < 32) {
-    // Which warps of the main kernel hold records of this pair?  The 32 lanes test a window of candidates
-    // around the cost estimate at once; only if the window's tile span does not cover the pair, lane 0
-    // walks the warps one by one.
-    const int lane = threadIdx.x;
-    const long long g_est = (unsigned)pair * (unsigned)p.tp.pair_cost / (p.tp.cost_quot ? p.tp.cost_quot : 1u);
-    const long long g0 = g_est - 3, gw = g0 + lane;
-    long long f0 = 0, f1 = 0;
-    bool on = false;
-    if (gw >= 0 && gw < W) {
-      mz_warp_tiles(p.tp, gw, &f0, &f1);
-      on = f0 < hi && f1 > lo && f0 < f1;
-    }
-    const unsigned mask = __ballot_sync(0xffffffffu, on);
-    // warp ranges are consecutive, so the window spans [f0 of its first warp, f1 of its last warp)
-    const int first_lane = g0 < 0 ? (int)-g0 : 0, last_lane = g0 + 31 > W - 1 ? (int)(W - 1 - g0) : 31;
-    const int w_lo = __shfl_sync(0xffffffffu, (int)f0, first_lane & 31), w_hi = __shfl_sync(0xffffffffu, (int)f1, last_lane & 31);
-    const bool open = first_lane > 31 || last_lane < 0 || w_lo > lo || w_hi < hi;
-    if (!open) {
-      if (on) s_slot[__popc(mask & ((1u << lane) - 1u))] = gw * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T));
-      if (lane == 0) { s_n = __popc(mask); s_first = g0 + __ffs(mask) - 1; }
-    } else if (lane == 0) {
-      long long g = g_est;
-      if (g >= W) g = W - 1;
-      for (mz_warp_tiles(p.tp, g, &f0, &f1); g > 0 && f0 > lo; mz_warp_tiles(p.tp, g, &f0, &f1)) --g;
-      for (; g + 1 < W && f1 <= lo; mz_warp_tiles(p.tp, g, &f0, &f1)) ++g;
-      s_first = g;
-      int n = 0;
-      for (long long gx = g; gx < W; ++gx) {
-        mz_warp_tiles(p.tp, gx, &f0, &f1);
-        if (f0 >= hi) break;
-        if (f1 <= lo || f0 >= f1) continue;
-        if (n < kMaxCombineSlots) s_slot[n] = gx * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T));
-        ++n;
-      }
-      s_n = n;
+  const unsigned quot = p.tp.cost_quot ? p.tp.cost_quot : 1u;
+  const unsigned c_lo = (unsigned)pair * (unsigned)p.tp.pair_cost, c_hi = c_lo + (unsigned)p.tp.pair_cost;
+  long long g_first = (long long)(c_lo / (quot + 1u)) - 1, g_last = (long long)((c_hi - 1u) / quot) + 1;
+  if (g_first < 0 || p.tp.cost_quot == 0) g_first = 0;
+  if (g_last > W - 1 || p.tp.cost_quot == 0) g_last = W - 1;     // more warps than cost units: no bound, test them all
+  const long long cand = g_last - g_first + 1;
+  const bool listed = cand <= kMaxCombineSlots && (long long)W * p.tp.max_segs < (1LL << 31);
+  if (listed) {
+    for (int i = threadIdx.x; i < cand; i += blockDim.x) {
+      long long f0, f1;
+      mz_warp_tiles(p.tp, g_first + i, &f0, &f1);
+      const bool on = f0 < hi && f1 > lo && f0 < f1;
+      s_slot[i] = on ? (int)((g_first + i) * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T))) : -1;
     }
   }
   // everything above is arithmetic on the plan; the records themselves are the main kernel's output
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncthreads();
-  const int n = s_n;
-  const bool listed = n <= kMaxCombineSlots;
-  // record slot of the i-th contributing warp (listed), or a walk over the warps (more than 64 splits)
+  const int n = (int)cand;
+  // more candidates than the list holds (a huge explicit split count): every thread walks them itself
   auto for_each_slot = [&](auto&& fn) {
-    if (listed) {
-      for (int i = 0; i < n; ++i) fn(s_slot[i]);
-    } else {
-      for (long long gw = s_first; gw < W; ++gw) {
-        long long f0, f1;
-        mz_warp_tiles(p.tp, gw, &f0, &f1);
-        if (f0 >= hi) break;
-        if (f1 <= lo || f0 >= f1) continue;
-        fn(gw * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T)));
-      }
+    for (long long gw = g_first; gw <= g_last; ++gw) {
+      long long f0, f1;
+      mz_warp_tiles(p.tp, gw, &f0, &f1);
+      if (f0 >= hi) break;
+      if (f1 <= lo || f0 >= f1) continue;
+      fn(gw * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T)));
     }
   };
-  for (int h = threadIdx.x >> 7; h < gqa; h += blockDim.x >> 7) {
+  const int quad = threadIdx.x >> 7, quads = blockDim.x >> 7;
+  for (int h = WIDE ? blockIdx.x % gqa : quad; h < gqa; h += WIDE ? gqa : quads) {
     const int d = threadIdx.x & 127;
     float mx = -INFINITY, lsum = 0.f, a = 0.f;
     if (listed) {
       // four records at a time: their loads are independent and in flight together; the running
       // maximum is carried along (one pass)
-      for (int i0 = 0; i0 < n; i0 += 4) {
+      for (int i0 = WIDE ? 4 * quad : 0; i0 < n; i0 += WIDE ? 4 * quads : 4) {
         float mi[4], li[4], ai[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const bool on = i0 + j < n;
-          const long long slot = on ? s_slot[i0 + j] * gqa + h : 0;
+          const int sl = i0 + j < n ? s_slot[i0 + j] : -1;
+          const bool on = sl >= 0;
+          const long long slot = on ? (long long)sl * gqa + h : 0;
           mi[j] = on ? p.part.m[slot] : -INFINITY;
           li[j] = on ? p.part.l[slot] : 0.f;
           ai[j] = on ? p.part.acc[slot * D + d] : 0.f;
@@ -614,7 +593,24 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
         }
         mx = m_new;
       }
-    } else {
+      if (WIDE) {
+        // the quads' states, merged in quad order by quad 0
+        s_part[quad][d] = a;
+        if (d == 0) { s_part[quad][128] = mx; s_part[quad][129] = lsum; }
+        __syncthreads();
+        if (quad != 0) continue;      // WIDE visits one head per CTA: nothing follows for these threads
+        float m_all = -INFINITY;
+        for (int k = 0; k < quads; ++k) m_all = fmaxf(m_all, s_part[k][128]);
+        lsum = 0.f; a = 0.f;
+        for (int k = 0; k < quads; ++k) {
+          const float mk = s_part[k][128];
+          const float wgt = mk > -INFINITY ? __expf(mk - m_all) : 0.f;
+          lsum = fmaf(s_part[k][129], wgt, lsum);
+          a = fmaf(s_part[k][d], wgt, a);
+        }
+        mx = m_all;
+      }
+    } else if (!WIDE || quad == 0) {
       for_each_slot([&](long long sl) { mx = fmaxf(mx, p.part.m[sl * gqa + h]); });
       for_each_slot([&](long long sl) {
         const long long slot = sl * gqa + h;
@@ -623,6 +619,8 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
         lsum = fmaf(p.part.l[slot], wgt, lsum);
         a = fmaf(p.part.acc[slot * D + d], wgt, a);
       });
+    } else {
+      continue;
     }
     const long long row = (long long)pair * gqa + h;
     if (o.out) mz_store_from_float(o.out, row * D + d, a / fmaxf(lsum, 1e-20f), o.out_dt);
@@ -755,14 +753,18 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
     W = pairs * splits_request;
   } else {
     W = (long long)sm_count * warps;              // one resident CTA per SM
-    const long long two_tiles = t.total_cost / (2 * t.cost_q);   // at least two packed tiles' worth per warp
-    if (W > two_tiles) W = two_tiles;
+    const long long one_tile = t.total_cost / t.cost_q;          // at least one packed tile's worth per warp
+    if (W > one_tile) W = one_tile;
     if (W < 1) W = 1;
   }
   if (W > (1LL << 30)) return mz_fail(MZ_ERR_ARG, "too many splits");
   t.total_warps = (int)W;
   t.cost_quot = (unsigned)(t.total_cost / W);
   t.cost_rem = (unsigned)(t.total_cost % W);
+  // a grid that does not fill the machine is spread over all SMs (a warp alone on its scheduler is faster)
+  if (W < (long long)sm_count * warps) warps = (int)((W + sm_count - 1) / sm_count);
+  t.warps_per_cta = warps;
+  t.smem_bytes = shared + per_warp * warps;
   t.ctas = (int)((W + warps - 1) / warps);
   // a warp's tiles start inside a cost interval of at most total_cost/W + 1
   const long long len = t.total_cost / W + 2;
@@ -796,8 +798,11 @@ int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t
   // programmatic dependent launch: the merge grid may start while the main kernel drains; it finds its
   // records (pure arithmetic) and then waits for the main grid's results (griddepcontrol.wait)
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(p.s.batch * p.s.kv_heads));
-  cfg.blockDim = dim3(128 * (p.gqa < 4 ? p.gqa : 4));
+  // many records per pair and few pairs: one CTA per (pair, head) with the records split over its quads
+  const long long pairs = (long long)p.s.batch * p.s.kv_heads;
+  const bool wide = p.tp.total_warps / pairs >= 24 && pairs * p.gqa <= 4096;
+  cfg.gridDim = dim3((unsigned)(wide ? pairs * p.gqa : pairs));
+  cfg.blockDim = dim3(wide ? 512 : 128 * (p.gqa < 4 ? p.gqa : 4));
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -805,7 +810,8 @@ int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_kernel, p, o));
+  if (wide) MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_kernel<true>, p, o));
+  else MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_kernel<false>, p, o));
   MZ_LAUNCH_CHECK("combine_tiles");
   return MZ_OK;
 }
