@@ -2,6 +2,7 @@
 // kernel dispatch, and the deterministic log-sum-exp combine.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "mz_decode.cuh"
 
@@ -34,14 +35,33 @@ __global__ void lse_combine_kernel(const float* __restrict__ m, const float* __r
   if (!out && threadIdx.x == 0) { out_m[row] = mx; out_l[row] = lsum; }
 }
 
-int g_sm_count = 0;
+// SM count of the current device (cached per device index: a process may drive unlike GPUs)
+constexpr int kMaxDevices = 64;
+std::mutex g_sm_mu;
+int g_sm_count[kMaxDevices] = {};
 int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) g_sm_count = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  std::lock_guard<std::mutex> lk(g_sm_mu);
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count[dev] = n;
   }
-  return g_sm_count;
+  return g_sm_count[dev];
+}
+
+// MZ_DECODE_KERNEL (read once, at the first call): "generic" routes every call to the shape-generic
+// kernel and "tiles" keeps the tensor-core kernel off, so that tests can cross-check the three kernels
+// against each other on the same device.  0 = automatic, 1 = generic, 2 = tiles.
+int kernel_override() {
+  static const int v = [] {
+    const char* e = std::getenv("MZ_DECODE_KERNEL");
+    if (e && std::strcmp(e, "generic") == 0) return 1;
+    if (e && std::strcmp(e, "tiles") == 0) return 2;
+    return 0;
+  }();
+  return v;
 }
 
 struct Plan {
@@ -76,11 +96,12 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   p.NG = (s->head_dim + s->group - 1) / s->group;
   p.eps = 1e-8f;
   p.table_k = p.table_v = nullptr;
-  // MZ_DECODE_KERNEL=generic routes every call to the shape-generic kernel (debugging aid)
-  const char* force = std::getenv("MZ_DECODE_KERNEL");
-  plan->tiles = mz_decode_tiles_supported(p) && !(force && std::strcmp(force, "generic") == 0);
+  const int force = kernel_override();
+  plan->tiles = force != 1 && mz_decode_tiles_supported(p);
   if (plan->tiles) {
-    if ((rc = mz_plan_tiles(p, a->splits, sm_count(), &plan->slots))) return rc;
+    if (force == 0 && mz_decode_mma_supported(p)) rc = mz_plan_mma(p, a->splits, sm_count(), &plan->slots);
+    else rc = mz_plan_tiles(p, a->splits, sm_count(), &plan->slots);
+    if (rc) return rc;
     p.splits = 0;
   } else {
     const int units = mz_decode_units_generic(*s);
@@ -114,7 +135,8 @@ int run_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
   p.part.m = (float*)a->workspace;
   p.part.l = p.part.m + plan->slots;
   p.part.acc = p.part.l + plan->slots;
-  return plan->tiles ? mz_launch_decode_tiles(p, st) : mz_launch_decode_generic(p, st);
+  if (!plan->tiles) return mz_launch_decode_generic(p, st);
+  return p.tp.kind == 1 ? mz_launch_decode_mma(p, st) : mz_launch_decode_tiles(p, st);
 }
 
 int finish(const Plan& plan, const MzDecodeOut& o, cudaStream_t st) {

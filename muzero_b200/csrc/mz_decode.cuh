@@ -25,6 +25,10 @@ struct MzTilesPlan {
   int packed_tiles, dense_tokens, cost_q, cost_d;
   long long pair_cost, total_cost;   // packed_tiles*cost_q + dense_tiles*cost_d ; pairs * pair_cost (< 2^31)
   unsigned cost_quot, cost_rem;      // total_cost / total_warps and the remainder
+  // which main kernel the plan is for (0: SIMT tiled kernel, 1: tensor-core kernel) and, for the latter,
+  // its per-warp staging size and the shared-window addresses of its two buffer pools
+  int kind;
+  unsigned stage_bytes, low_base, high_base;
 };
 
 // Number of tiles (in flat order: pair-major, packed tiles before residual tiles) whose start cost
@@ -79,3 +83,9 @@ bool mz_decode_tiles_supported(const MzDecodeParams& p);
 int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots);
 int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st);
 int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t st);
+
+// tensor-core kernel: head_dim 128, group 64, 2- or 4-bit codes, gqa in {1,2,4}; shares the partition,
+// the partial records and the merge kernel with the tiled kernel
+bool mz_decode_mma_supported(const MzDecodeParams& p);
+int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots);
+int mz_launch_decode_mma(const MzDecodeParams& p, cudaStream_t st);

@@ -9,7 +9,6 @@
 // head are served from one read of the tile, softmax is kept online per warp in base 2, and
 // each (warp, pair) segment ends in one partial (m, l, acc) record.  A second small kernel
 // merges the records of a pair deterministically.  No atomics, no inter-CTA waits.
-#include <cstdlib>
 #include <type_traits>
 
 #include "mz_tiles_common.cuh"
@@ -723,10 +722,8 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
   if (warps < 1) return mz_fail(MZ_ERR_UNSUPPORTED, "tile does not fit shared memory");
   const int max_warps = p.gqa > 4 ? 8 : 12;      // Cfg::MAX_WARPS
   if (warps > max_warps) warps = max_warps;
-  if (const char* e = std::getenv("MZ_TILES_WARPS")) {   // tuning aid: fewer warps per CTA
-    const int w = atoi(e);
-    if (w >= 1 && w < warps) warps = w;
-  }
+  t.kind = 0;
+  t.stage_bytes = t.low_base = t.high_base = 0;
   t.warps_per_cta = warps;
   t.smem_per_warp = per_warp;
   t.smem_bytes = shared + per_warp * warps;
@@ -738,10 +735,6 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
   // measured on B200 (4-bit and 2-bit caches, group 64)
   t.cost_q = s.group + 10;
   t.cost_d = t.dense_tokens + 16;
-  if (const char* e = std::getenv("MZ_TILES_DENSE_COST")) {   // tuning aid
-    const int c = atoi(e);
-    if (c >= 1 && c <= 4096) t.cost_d = c;
-  }
   const long long pairs = (long long)s.batch * s.kv_heads;
   t.total_tiles = pairs * t.tiles_per_pair;
   t.pair_cost = (long long)t.packed_tiles * t.cost_q + (long long)dense_tiles * t.cost_d;
@@ -774,11 +767,6 @@ int mz_plan_tiles(MzDecodeParams& p, int splits_request, int sm_count, size_t* s
 }
 
 int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st) {
-#ifdef MZ_TILES_HEADLINE_ONLY   // fast experimental builds: only the two headline shapes
-  if (p.s.group == 64 && p.gqa == 4 && p.s.bits == 4) return mzt::launch_one<4, 64, 4>(p, st);
-  if (p.s.group == 64 && p.gqa == 4 && p.s.bits == 2) return mzt::launch_one<2, 64, 4>(p, st);
-  return mz_fail(MZ_ERR_UNSUPPORTED, "experimental build");
-#else
   switch (p.s.bits) {
     case 1: return mzt::launch_group<1>(p, st);
     case 2: return mzt::launch_group<2>(p, st);
@@ -790,7 +778,6 @@ int mz_launch_decode_tiles(const MzDecodeParams& p, cudaStream_t st) {
     case 8: return mzt::launch_group<8>(p, st);
   }
   return mz_fail(MZ_ERR_UNSUPPORTED, "bits %d", p.s.bits);
-#endif
 }
 
 int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t st) {

@@ -73,16 +73,11 @@ __device__ __forceinline__ void warp_copy_async(uint8_t* dst, const uint8_t* src
 
 // packed fp32 pair: d += a * b on both halves (one issue slot on sm_100)
 __device__ __forceinline__ void ffma2(float2& d, const float2 a, const float2 b) {
-#if defined(MZ_NO_F32X2)
-  d.x = fmaf(a.x, b.x, d.x);
-  d.y = fmaf(a.y, b.y, d.y);
-#else
   unsigned long long dd = *reinterpret_cast<unsigned long long*>(&d);
   const unsigned long long aa = *reinterpret_cast<const unsigned long long*>(&a);
   const unsigned long long bb = *reinterpret_cast<const unsigned long long*>(&b);
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(dd) : "l"(aa), "l"(bb));
   d = *reinterpret_cast<float2*>(&dd);
-#endif
 }
 
 __device__ __forceinline__ float ex2f(float x) {
