@@ -162,6 +162,14 @@ typedef struct mz_decode_args {
 size_t mz_decode_workspace_bytes(const mz_decode_args* args);
 
 /*
+ * Bytes of workspace that suffice for mz_decode_attention / mz_decode_step with this batch, head
+ * counts, head_dim and `splits`, whatever the number of cached tokens: a host that keeps one argument
+ * block per layer sizes its scratch once with this instead of asking before every step.  0 = invalid
+ * arguments.  Replaces: the per-call allocations of partial buffers in muzero/cache/attention.py:107-109,130-132.
+ */
+size_t mz_decode_workspace_bound(const mz_decode_args* args);
+
+/*
  * Fused decode attention over packed K/V + residual window with GQA:
  * QK, online softmax, AV per sequence split, then a deterministic
  * log-sum-exp combine.  fp32 accumulation throughout.

@@ -42,11 +42,14 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 
 def build_decode_args(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor],
-                      out: Optional[torch.Tensor], *, splits: int = 0, step: Optional[tuple[int, int]] = None) -> DecodeArgs:
+                      out: Optional[torch.Tensor], *, splits: int = 0, step: Optional[tuple[int, int]] = None,
+                      bound: bool = False) -> DecodeArgs:
     """Fills the C argument block for one decode call on ``layer``.
 
     ``step=(residual_length, flush_unit)``: the block is for ``mz_decode_step``, i.e. the mask must
-    cover one more token and the workspace is sized for the store as it will be after the step."""
+    cover one more token and the workspace is sized for the store as it will be after the step.
+    ``bound=True``: the workspace is sized for any number of cached tokens (``mz_decode_workspace_bound``),
+    so that the block can be reused for later steps."""
     if not query.is_cuda:
         raise MuZeroKernelError("decode attention needs CUDA tensors; this package has no CPU path")
     if query.dtype != layer.dtype:
@@ -81,7 +84,9 @@ def build_decode_args(layer, query: torch.Tensor, scaling: float, attention_mask
         a.out = out.data_ptr()
         a.out_dtype = dtype_code(out.dtype)
     lib = load_mu_zero_cuda_extension()
-    if step:
+    if bound:
+        need = lib.mz_decode_workspace_bound(ctypes.byref(a))
+    elif step:
         need = lib.mz_decode_step_workspace_bytes(ctypes.byref(a), int(step[0]), int(step[1]))
     else:
         need = lib.mz_decode_workspace_bytes(ctypes.byref(a))

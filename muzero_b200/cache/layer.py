@@ -59,8 +59,13 @@ class MuZeroCacheLayer:
         self.device = None
         self.k_head_dim = self.v_head_dim = None
         self.v_head_dim_padded = self.v_num_groups = None
-        self.keys = None
-        self.values = None
+        self._keys = None
+        self._values = None
+        self._window_stale = False     # decode_step moved the window; the views are rebuilt on first use
+        self._window_len = 0           # residual tokens after the last one-call decode step
+        self._step_args = None         # C argument block kept across steady-state decode steps
+        self._step_base = 0            # _res_start at the time the block was built
+        self._step_ws_bound = 0
         self._key_buffer = None
         self._value_buffer = None
         self._buffer_capacity = 0
@@ -73,6 +78,40 @@ class MuZeroCacheLayer:
         self._bufs: dict[str, torch.Tensor] = {}
         self._key_group_count = 0
         self._value_storage_len = 0
+
+    # `keys` / `values` (the residual window, attribute names of the reference) are views into the window
+    # buffers; the one-call decode step only moves counters and leaves rebuilding the views to the first reader
+    @property
+    def keys(self):
+        if self._window_stale:
+            self._rebuild_window_views()
+        return self._keys
+
+    @keys.setter
+    def keys(self, value):
+        if self._window_stale:
+            self._rebuild_window_views()
+        self._keys = value
+        self._step_args = None
+
+    @property
+    def values(self):
+        if self._window_stale:
+            self._rebuild_window_views()
+        return self._values
+
+    @values.setter
+    def values(self, value):
+        if self._window_stale:
+            self._rebuild_window_views()
+        self._values = value
+        self._step_args = None
+
+    def _rebuild_window_views(self) -> None:
+        self._window_stale = False
+        a, n = self._res_start, self._window_len
+        self._keys = self._key_buffer[:, :, a:a + n]
+        self._values = self._value_buffer[:, :, a + self._value_lead:a + n]
 
     # ------------------------------------------------------------------ init
     def lazy_initialization(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
@@ -102,12 +141,14 @@ class MuZeroCacheLayer:
         """C descriptor of the current state (pointers, strides, counters)."""
         s = KVStore()
         k = self.keys
-        s.batch, s.kv_heads, s.head_dim = k.shape[0], k.shape[1], self.k_head_dim
+        b = self._bufs
+        # the batch comes from the store when there is one: an empty residual window may be a bare tensor
+        s.batch, s.kv_heads = (b["pk"].shape[0], b["pk"].shape[1]) if b else (k.shape[0], k.shape[1])
+        s.head_dim = self.k_head_dim
         s.group, s.bits = self.q_group_size, self.nbits
         s.meta_dtype, s.kv_dtype = dtype_code(self.amax_dtype), dtype_code(self.dtype)
         s.alpha_key = float(self._selected_alpha_key if self._selected_alpha_key is not None else 2.0)
         s.alpha_value = float(self._selected_alpha_value if self._selected_alpha_value is not None else 2.0)
-        b = self._bufs
         if b:
             s.packed_k, s.k_mn, s.k_scale = b["pk"].data_ptr(), b["kmn"].data_ptr(), b["ksc"].data_ptr()
             s.pk_stride_b, s.pk_stride_h = b["pk"].stride(0), b["pk"].stride(1)
@@ -161,6 +202,10 @@ class MuZeroCacheLayer:
         if self.keys.numel() == 0 and self._key_buffer is None:
             self.keys, self.values = key_states, value_states      # alias the caller's block
             self._res_start = 0
+            if key_states.stride(-1) != 1 or value_states.stride(-1) != 1 or key_states.stride() != value_states.stride():
+                # the kernels address keys and values of the window with one set of strides: a block whose two
+                # tensors are laid out differently is copied into the layer's own buffers instead
+                self._rehome_residual(n_new + 1)
             return
         if n_new == 1:
             cur = int(self.keys.shape[2])
@@ -240,6 +285,7 @@ class MuZeroCacheLayer:
             for name in ("pv", "vmn", "vsc"):
                 new[name][:, :, :vt].copy_(self._bufs[name][:, :, :vt])
         self._bufs = new
+        self._step_args = None
         self._refresh_views()
 
     def _refresh_views(self) -> None:
@@ -255,6 +301,7 @@ class MuZeroCacheLayer:
     def _adopt_store(self, tensors: dict[str, torch.Tensor]) -> None:
         """Replaces the store by exact-size tensors (after batch reindexing / device moves)."""
         self._bufs = {k: v.contiguous() for k, v in tensors.items()}
+        self._step_args = None
         self._refresh_views()
 
     # ------------------------------------------------------------------ alpha
@@ -358,7 +405,7 @@ class MuZeroCacheLayer:
         attention (reference: muzero/cache/layer.py:407-459 and muzero/cache/attention.py:48-295), but in the
         steady state (window inside its buffer, store with room, alphas chosen) it is a single C call,
         ``mz_decode_step``.  Anything else takes the two-call route.  Returns ``[B,1,H,D]``."""
-        from .attention import build_decode_args, decode_attention
+        from .attention import build_decode_args, decode_attention, _workspace
         g = self.q_group_size
         fast = (self.is_initialized and self._key_buffer is not None and key_states.shape[2] == 1 and key_states.is_cuda
                 and key_states.dtype == self.dtype and not self.cfg.logq_compatible_layout
@@ -366,7 +413,8 @@ class MuZeroCacheLayer:
                 and key_states.stride()[:2] == value_states.stride()[:2])
         unit = g if self.cfg.decode_flush_by_group else 4 * g
         if fast:
-            cur = int(self.keys.shape[2])
+            args = self._step_args
+            cur = args.store.res_len if args is not None else int(self.keys.shape[2])
             if self._res_start + cur + 1 > self._buffer_capacity:
                 fast = False                      # the window has to move back to the front of its buffer
             excess = cur + 1 - self.residual_length
@@ -381,20 +429,42 @@ class MuZeroCacheLayer:
             return decode_attention(self, query, scaling, attention_mask)
         b, h, _, d = query.shape
         out = torch.empty((b, 1, h, d), dtype=query.dtype, device=query.device)
-        args = build_decode_args(self, query, scaling, attention_mask, out, step=(self.residual_length, unit))
+        lib = load_mu_zero_cuda_extension()
+        args = self._step_args
+        if attention_mask is not None or args is None or query.stride(-1) != 1 or query.dtype != self.dtype:
+            # (re)build the argument block: pointers, strides and counters of the current state.  With a mask
+            # the block is built per call (the mask tensor may be converted and has to stay alive).
+            args = build_decode_args(self, query, scaling, attention_mask, out, step=(self.residual_length, unit), bound=True)
+            self._step_base = self._res_start
+            self._step_ws_bound = args.workspace_bytes
+            self._step_args = args if attention_mask is None else None
+        else:
+            # steady state: the block kept from the last step already holds the advanced counters
+            args.query, args.q_stride_b, args.q_stride_h = query.data_ptr(), query.stride(0), query.stride(1)
+            args.q_heads, args.scaling = h, float(scaling)
+            args.out, args.out_dtype = out.data_ptr(), dtype_code(out.dtype)
+            ws = _workspace(query.device, self._step_ws_bound)
+            args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
         with torch.cuda.device(self.device):
-            check(load_mu_zero_cuda_extension().mz_decode_step(
+            rc = lib.mz_decode_step(
                 ctypes.byref(args), key_states.data_ptr(), value_states.data_ptr(), key_states.stride(0), key_states.stride(1),
                 self.residual_length, unit, int(self._bufs["pk"].shape[2]) if self._bufs else 0,
-                self._buffer_capacity - self._res_start, self.amax_eps, stream_ptr(self.device)), "mz_decode_step")
+                self._buffer_capacity - self._step_base, self.amax_eps, stream_ptr(self.device))
+        if rc != 0:
+            self._step_args = None                # nothing moved (the library commits counters last); rebuild next time
+            check(rc, "mz_decode_step")
         st = args.store
         flushed = st.k_groups != self._key_group_count
-        self._res_start += st.res_start            # the descriptor's window starts at its own pointer
+        self._res_start = self._step_base + st.res_start     # the block's window starts at its own pointer
         self._key_group_count, self._value_storage_len = st.k_groups, st.v_tokens
-        a = self._res_start
-        self.keys = self._key_buffer[:, :, a:a + st.res_len]
-        self.values = self._value_buffer[:, :, a:a + st.res_len]
+        self._window_len = st.res_len
         self.cumulative_length += 1
+        if self._step_args is None:
+            a = self._res_start
+            self._keys = self._key_buffer[:, :, a:a + st.res_len]
+            self._values = self._value_buffer[:, :, a:a + st.res_len]
+        else:
+            self._window_stale = True
         if flushed:
             self._refresh_views()
         return out
@@ -438,7 +508,9 @@ class MuZeroCacheLayer:
             self.cumulative_length = max_length
 
     def _reindex_batch(self, fn) -> None:
-        if self.keys is not None and self.keys.numel():
+        if self.keys is not None and self.keys.dim() == 4:
+            # also with zero residual tokens (residual_length=0 right after a flush): the window's shape
+            # carries the batch size, and its old buffers belong to the old batch
             self.keys, self.values = fn(self.keys).contiguous(), fn(self.values).contiguous()
             self._key_buffer = self._value_buffer = None
             self._buffer_capacity, self._res_start = 0, 0

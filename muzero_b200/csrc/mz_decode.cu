@@ -64,12 +64,7 @@ int kernel_override() {
   return v;
 }
 
-struct Plan {
-  MzDecodeParams p;
-  bool tiles;
-  size_t slots;     // partial records
-  size_t ws_bytes;
-};
+using Plan = MzDecodePlan;
 
 int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   MZ_REQUIRE(a != nullptr, "args is NULL");
@@ -125,9 +120,8 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   return MZ_OK;
 }
 
-int run_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
-  int rc = make_plan(a, plan, true);
-  if (rc) return rc;
+// launches the main kernel of an existing plan (the workspace is checked here)
+int launch_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
   if (a->workspace == nullptr || a->workspace_bytes < plan->ws_bytes)
     return mz_fail(MZ_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", plan->ws_bytes, a->workspace_bytes);
   MZ_REQUIRE((uintptr_t)a->workspace % 16 == 0, "workspace must be 16-byte aligned");
@@ -137,6 +131,12 @@ int run_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
   p.part.acc = p.part.l + plan->slots;
   if (!plan->tiles) return mz_launch_decode_generic(p, st);
   return p.tp.kind == 1 ? mz_launch_decode_mma(p, st) : mz_launch_decode_tiles(p, st);
+}
+
+int run_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
+  int rc = make_plan(a, plan, true);
+  if (rc) return rc;
+  return launch_partials(a, plan, st);
 }
 
 int finish(const Plan& plan, const MzDecodeOut& o, cudaStream_t st) {
@@ -160,6 +160,36 @@ int mz_decode_plan_info(const mz_decode_args* args, size_t* ws_bytes, int* needs
   *ws_bytes = plan.ws_bytes;
   *needs_tables = plan.tiles ? 0 : 1;
   return MZ_OK;
+}
+
+// Internal (used by mz_decode_step): validation and planning of a normalising call, then its launches.
+int mz_decode_plan(const mz_decode_args* a, MzDecodePlan* plan) {
+  MZ_REQUIRE(a != nullptr && a->out != nullptr && mz_dtype_ok(a->out_dtype), "bad output");
+  return make_plan(a, plan, true);
+}
+int mz_decode_run_plan(const mz_decode_args* a, MzDecodePlan* plan, cudaStream_t st) {
+  int rc = launch_partials(a, plan, st);
+  if (rc) return rc;
+  const MzDecodeOut o = {a->out, a->out_dtype, nullptr, nullptr, nullptr};
+  return finish(*plan, o, st);
+}
+
+extern "C" size_t mz_decode_workspace_bound(const mz_decode_args* a) {
+  if (a == nullptr || mz_check_store_basic(&a->store) != MZ_OK) return 0;
+  const mz_kv_store& s = a->store;
+  if (a->q_heads <= 0 || a->q_heads % s.kv_heads != 0 || a->splits < 0) {
+    mz_fail(MZ_ERR_ARG, "q_heads %d / splits %d", a->q_heads, a->splits);
+    return 0;
+  }
+  const long long pairs = (long long)s.batch * s.kv_heads, gqa = a->q_heads / s.kv_heads;
+  const long long sms = sm_count();
+  // tiled kernels: slots = W * max_segs * gqa <= gqa * (pairs + 3 W), W <= 12 warps per SM (or pairs * splits)
+  const long long w_max = a->splits > 0 ? pairs * a->splits : sms * 12;
+  const long long tiled = gqa * (pairs + 3 * w_max);
+  // generic kernel: one slot per (batch, head, split)
+  const long long splits = a->splits > 0 ? a->splits : (2 * sms * 4 + pairs - 1) / pairs;
+  const long long generic = (long long)s.batch * a->q_heads * (splits < 1 ? 1 : splits);
+  return (size_t)(tiled > generic ? tiled : generic) * sizeof(float) * (2 + (size_t)s.head_dim);
 }
 
 extern "C" size_t mz_decode_workspace_bytes(const mz_decode_args* args) {

@@ -74,6 +74,17 @@ struct MzDecodeOut {
   float* m; float* l; float* acc;
 };
 
+// A validated call: which kernel runs, its parameters, the partial records and scratch bytes it needs.
+struct MzDecodePlan {
+  MzDecodeParams p;
+  bool tiles;
+  size_t slots;     // partial records
+  size_t ws_bytes;
+};
+// validation + planning of mz_decode_attention(a), and the launches of an existing plan
+int mz_decode_plan(const mz_decode_args* a, MzDecodePlan* plan);
+int mz_decode_run_plan(const mz_decode_args* a, MzDecodePlan* plan, cudaStream_t st);
+
 // generic kernel: any bits / group / head_dim<=512 / gqa<=16
 int mz_launch_decode_generic(const MzDecodeParams& p, cudaStream_t st);
 int mz_decode_units_generic(const mz_kv_store& s);

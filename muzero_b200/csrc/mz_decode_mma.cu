@@ -18,7 +18,10 @@
 //     at shared-window address 65536, so that the address of a lookup is one byte permute:
 //     byte 1 of the address <- (zc << BITS | e)
 //   * the B operand holds the folded query (keys) or folded probabilities (values); its 8 columns are
-//     4 heads x {high part, exact fp16 remainder} for the keys, 4 heads x {value, 0} for the values
+//     4 heads x {product rounded to fp16, its exact fp16 remainder (+ the remainder of the probability)}
+//   * the idle half of a table entry (u- of a code above the zero code, u+ of one below) carries the fp16
+//     remainder of the active half, pre-scaled by the nominal ratio of the two side constants of the
+//     zero-code bin, which recovers most of the table's own fp16 rounding
 //   * M rows are tokens (keys) or channels (values), permuted so that one 32-bit load of packed codes
 //     feeds a thread's rows of four M tiles.
 // Residual (un-quantized) tiles of 16 tokens run through the same tensor-core path with the cache's own
@@ -46,7 +49,7 @@ constexpr int Z_BYTES = 128;                // zero codes of one tile side: [t][
 constexpr int RI_BYTES = Z_BYTES + 512;     // + fold constants: 64 x {half2(Bup, Bdn) of slot 0, of slot 1}
 constexpr int A_BYTES = 512;                // per-row constant A (fp32) of one tile side
 constexpr int PBUF_BYTES = 1024;            // folded-probability source: [8 k-blocks][32 lanes] half2
-constexpr int DBUF_BYTES = 256;             // residual-tile probabilities [16 tokens][4 heads] fp32
+constexpr int DBUF_BYTES = 256;             // residual-tile probabilities [16 tokens][4 heads] fp32; shares the value side's A array
 constexpr int MAX_WARPS = 12;
 
 // ---- shared memory by shared-window address (no generic-address arithmetic in the loops) ----
@@ -172,6 +175,13 @@ __device__ __forceinline__ void zero_words(uint32_t zreg, int b0, uint32_t& z0, 
   }
 }
 
+// One B-operand register of a lane: x * B for the pair B = (Bup, Bdn).  mask = 0 (even column): the fp16
+// product; mask = all ones (odd column): what that rounding dropped, exactly.
+__device__ __forceinline__ uint32_t fold_pair(__half2 x, uint32_t B, uint32_t mask) {
+  const uint32_t h = h2_bits(__hmul2(x, bits_h2(B))) & mask;
+  return h2_bits(__hfma2(x, bits_h2(B), __hneg2(bits_h2(h))));
+}
+
 // swizzle of the folded-probability buffer: word (j, t', g') lives at j*32 + ((8t' + g') ^ pswz(j)), which
 // spreads both the softmax lanes' stores (j = their g) and the fold's loads over all banks
 __host__ __device__ constexpr int pswz(int j) { return (j & 1) | (((j >> 1) & 3) << 3); }
@@ -198,13 +208,21 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
     const int zc = idx >> BITS, e = idx & TOP;
     const float alpha = which ? s.alpha_value : s.alpha_key;
     const float lb = log1pf(alpha);
+    // nominal ratio Bdn / Bup of a row in this zero-code bin (anchor at the bin centre); the end bins have
+    // codes on one side only and prep_rows makes their two constants equal
+    const float zac = (float)zc / (float)TOP;
+    const float ratio = (zc == 0 || zc == TOP) ? 1.0f : zac / (1.0f - zac);
     __half2 ent;
     if (e >= zc) {
       const int up = max(TOP - zc, 1);
-      ent = __floats2half2_rn(expm1f((float)min(e - zc, up) / (float)up * lb) / alpha, 0.f);
+      const float u = expm1f((float)min(e - zc, up) / (float)up * lb) / alpha;
+      const float uh = __half2float(__float2half_rn(u));
+      ent = __floats2half2_rn(uh, (u - uh) / ratio);
     } else {
       const int dn = max(zc, 1);
-      ent = __floats2half2_rn(0.f, -expm1f((float)(zc - e) / (float)dn * lb) / alpha);
+      const float u = -expm1f((float)(zc - e) / (float)dn * lb) / alpha;
+      const float uh = __half2float(__float2half_rn(u));
+      ent = __floats2half2_rn((u - uh) * ratio, uh);
     }
     const uint32_t bits = h2_bits(ent);
     const uint32_t row = TBL + idx * 256 + which * 128;
@@ -224,13 +242,13 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
   Layout L;
   L.kbuf = p.tp.low_base + warp * SB;
   L.aK = p.tp.low_base + nw * SB + warp * A_BYTES;
-  const uint32_t hb = p.tp.high_base + warp * (SB + 2 * RI_BYTES + A_BYTES + PBUF_BYTES + DBUF_BYTES);
+  const uint32_t hb = p.tp.high_base + warp * (SB + 2 * RI_BYTES + A_BYTES + PBUF_BYTES);
   L.vbuf = hb;
   L.riK = hb + SB;
   L.riV = L.riK + RI_BYTES;
   L.aV = L.riV + RI_BYTES;
   L.pbuf = L.aV + A_BYTES;
-  L.dbuf = L.pbuf + PBUF_BYTES;
+  L.dbuf = L.aV;                // residual tiles have no per-row constants
   for (int i = lane; i < PBUF_BYTES / 4; i += 32) sts32(L.pbuf + i * 4, 0u);   // the odd columns stay zero for good
   __syncthreads();
   if (gw >= W || f0 >= f1) return;
@@ -323,8 +341,12 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
       const int zc = __float2int_rn(__fmul_rn(anchor, (float)TOP));
       float A = fmaf(span, anchor, lo);
       if (fabsf(A) <= 9.5367431640625e-7f * fmaxf(fabsf(lo), span)) A = 0.0f;
-      const float Bup = fminf(span * fmaxf(1.0f - anchor, 1e-8f), 65504.f);
-      const float Bdn = fminf(span * fmaxf(anchor, 1e-8f), 65504.f);
+      float Bup = fminf(span * fmaxf(1.0f - anchor, 1e-8f), 65504.f);
+      float Bdn = fminf(span * fmaxf(anchor, 1e-8f), 65504.f);
+      // a row whose zero code is the first / last code has no codes on the other side: that side's constant
+      // only ever multiplies the remainder half of the table entries (see the table)
+      if (zc == 0) Bdn = Bup;
+      if (zc == TOP) Bup = Bdn;
       any |= A != 0.0f;
       const int pos = values ? (r >> 1) : r, grp = values ? (r & 1) : 0;
       const int j = pos >> 3, slot = (pos >> 2) & 1, tt = pos & 3;
@@ -481,12 +503,9 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
           uint32_t z0, z1;
           zero_words<BITS>(zr[j >> 1], 2 * (j & 1), z0, z1);
           lookups16<BITS>(spread_codes<BITS>(w[0], w[1], z0, z1), lbK, a);
-          // fold: even columns q*B rounded to fp16, odd columns the exact remainder of that rounding
-          const __half2 q0 = dup_lo(qh2[j]), q1 = dup_hi(qh2[j]);
-          const __half2 B0 = bits_h2(B.x), B1 = bits_h2(B.y);
-          const uint32_t h0 = h2_bits(__hmul2(q0, B0)) & rem_mask, h1 = h2_bits(__hmul2(q1, B1)) & rem_mask;
-          b[0] = h2_bits(__hfma2(q0, B0, __hneg2(bits_h2(h0))));
-          b[1] = h2_bits(__hfma2(q1, B1, __hneg2(bits_h2(h1))));
+          // fold q * B: even columns the product rounded to fp16, odd columns what that rounding dropped
+          b[0] = fold_pair(dup_lo(qh2[j]), B.x, rem_mask);
+          b[1] = fold_pair(dup_hi(qh2[j]), B.y, rem_mask);
         };
         load_block(0, cw[0], Bw[0]);
         load_block(1, cw[1], Bw[1]);
@@ -533,9 +552,15 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
       }
       softmax_update(sv);
       if (t < GQA) {
+        // probabilities as fp16 pairs: column 2t the rounded value, column 2t+1 its remainder
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          sts32(L.pbuf + g * 128 + (((8 * i + 2 * t) ^ pswz(g)) << 2), h2_bits(__floats2half2_rn(sv[i], sv[i + 4])));
+        for (int i = 0; i < 4; ++i) {
+          const __half2 ph = __floats2half2_rn(sv[i], sv[i + 4]);
+          const float2 phf = __half22float2(ph);
+          const uint32_t wa = L.pbuf + g * 128;
+          sts32(wa + (((8 * i + 2 * t) ^ pswz(g)) << 2), h2_bits(ph));
+          sts32(wa + (((8 * i + 2 * t + 1) ^ pswz(g)) << 2), h2_bits(__floats2half2_rn(sv[i] - phf.x, sv[i + 4] - phf.y)));
+        }
       }
       cp_async_wait<1>();
       warp_sync();                  // value tile landed; probabilities visible
@@ -545,21 +570,24 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
       if (hasAV && t < GQA) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          // the probability as the tensor cores see it (fp16)
-          const float pi = __half2float(__float2half_rn(sv[i]));
+          const float pi = sv[i];
           base_v[0] = fmaf(pi, ldsf(L.aV + (8 * g + i) * 4), base_v[0]);
           base_v[1] = fmaf(pi, ldsf(L.aV + (64 + 8 * g + i) * 4), base_v[1]);
         }
       }
       {
-        const int lw = 8 * t + g;     // this lane's word of a folded-probability block
-        uint32_t zr[8], pw[8];        // zero codes of this lane's 32 rows; half2(p[8j+t], p[8j+4+t]) of head hq, or 0
+        // this lane folds for head hq: the rounded probabilities sit in column 2*hq, their remainders in 2*hq+1
+        const int lwh = 8 * t + (g & ~1), lwl = lwh + 1;
+        uint32_t zr[8], pwh[8], pwl[8];   // zero codes of this lane's 32 rows; half2(p[8j+t], p[8j+4+t]) high parts / remainders
         {
           const uint4 za = lds128(L.riV + t * 32), zb = lds128(L.riV + t * 32 + 16);
           zr[0] = za.x; zr[1] = za.y; zr[2] = za.z; zr[3] = za.w; zr[4] = zb.x; zr[5] = zb.y; zr[6] = zb.z; zr[7] = zb.w;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) pw[j] = lds32(L.pbuf + j * 128 + ((lw ^ pswz(j)) << 2));
+        for (int j = 0; j < 8; ++j) {
+          pwh[j] = lds32(L.pbuf + j * 128 + ((lwh ^ pswz(j)) << 2));
+          pwl[j] = lds32(L.pbuf + j * 128 + ((lwl ^ pswz(j)) << 2)) & rem_mask;
+        }
         // 16 reduction blocks: block = 2*j + group; same two-stage pipeline as the keys
         uint32_t cw[3][2], av[2][16], bf[2][2];
         uint2 Bw[3];
@@ -580,8 +608,9 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
           uint32_t z0, z1;
           zero_words<BITS>(zr[j], 2 * grp, z0, z1);
           lookups16<BITS>(spread_codes<BITS>(w[0], w[1], z0, z1), lbV, a);
-          b[0] = h2_bits(__hmul2(dup_lo(pw[j]), bits_h2(B.x)));
-          b[1] = h2_bits(__hmul2(dup_hi(pw[j]), bits_h2(B.y)));
+          // fold (ph + pl) * B: even columns fp16(ph * B), odd columns its remainder + pl * B
+          b[0] = h2_bits(__hfma2(dup_lo(pwl[j]), bits_h2(B.x), bits_h2(fold_pair(dup_lo(pwh[j]), B.x, rem_mask))));
+          b[1] = h2_bits(__hfma2(dup_hi(pwl[j]), bits_h2(B.y), bits_h2(fold_pair(dup_hi(pwh[j]), B.y, rem_mask))));
         };
         load_block(0, cw[0], Bw[0]);
         load_block(1, cw[1], Bw[1]);
@@ -741,7 +770,7 @@ int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slo
   const unsigned low_base = (wb + 127u) & ~127u;
   const unsigned high_base = mzm::TBL + table_bytes;
   const unsigned per_low = sb + mzm::A_BYTES;
-  const unsigned per_high = sb + 2 * mzm::RI_BYTES + mzm::A_BYTES + mzm::PBUF_BYTES + mzm::DBUF_BYTES;
+  const unsigned per_high = sb + 2 * mzm::RI_BYTES + mzm::A_BYTES + mzm::PBUF_BYTES;
   const unsigned window_end = wb + 227u * 1024u;      // the most dynamic shared memory a block may ask for
   int warps = mzm::MAX_WARPS;
   if ((unsigned)warps > (mzm::TBL - low_base) / per_low) warps = (int)((mzm::TBL - low_base) / per_low);

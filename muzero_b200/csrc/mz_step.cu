@@ -4,7 +4,7 @@
 // run the fused decode attention over the updated cache.  It is the sequence the host otherwise
 // drives from Python (append, flush check, flush, attention); the counters of args->store are
 // advanced in place so that the host can mirror them.
-#include "mz_common.cuh"
+#include "mz_decode.cuh"
 
 namespace {
 // counters of the store after the append and the flush the step would do; returns the tokens flushed
@@ -37,22 +37,30 @@ extern "C" int mz_decode_step(mz_decode_args* a, const void* k_new, const void* 
   if (s->res_start + s->res_len + 1 > window_capacity)
     return mz_fail(MZ_ERR_WORKSPACE, "residual window ends at row %d of %d: move it to the front of its buffer first",
                    s->res_start + s->res_len, window_capacity);
+  // everything is validated and planned on the store as it will be after the step, before anything is
+  // launched; the caller's counters move only when all launches were accepted
   mz_decode_args post = *a;
   const int n = advance(&post.store, residual_length, flush_unit);
-  const size_t need = mz_decode_workspace_bytes(&post);
-  if (need == 0) return MZ_ERR_ARG;                      // message left by the size query
-  if (a->workspace == nullptr || a->workspace_bytes < need)
-    return mz_fail(MZ_ERR_WORKSPACE, "workspace of %zu bytes needed after the step, %zu given", need, a->workspace_bytes);
+  MzDecodePlan plan;
+  int rc = mz_decode_plan(&post, &plan);
+  if (rc) return rc;
+  if (a->workspace == nullptr || a->workspace_bytes < plan.ws_bytes)
+    return mz_fail(MZ_ERR_WORKSPACE, "workspace of %zu bytes needed after the step, %zu given", plan.ws_bytes, a->workspace_bytes);
+  MZ_REQUIRE((uintptr_t)a->workspace % 16 == 0, "workspace must be 16-byte aligned");
+  MZ_REQUIRE(k_new != nullptr && v_new != nullptr, "new key/value is NULL");
   if (n > 0 && s->k_groups + n / s->group > group_capacity)
     return mz_fail(MZ_ERR_WORKSPACE, "store holds %d of %d key groups, the flush needs %d more", s->k_groups, group_capacity,
                    n / s->group);
-  int rc = mz_append_kv(s, k_new, v_new, new_stride_b, new_stride_h, stream);
+  rc = mz_append_kv(s, k_new, v_new, new_stride_b, new_stride_h, stream);
   if (rc) return rc;
-  s->res_len += 1;
   if (n > 0) {
-    rc = mz_flush_kv(s, n, eps, stream);
+    mz_kv_store appended = *s;
+    appended.res_len += 1;
+    rc = mz_flush_kv(&appended, n, eps, stream);
     if (rc) return rc;
   }
+  rc = mz_decode_run_plan(&post, &plan, (cudaStream_t)stream);
+  if (rc) return rc;
   *s = post.store;
-  return mz_decode_attention(a, stream);
+  return MZ_OK;
 }

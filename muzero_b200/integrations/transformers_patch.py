@@ -41,6 +41,11 @@ class MuZeroCache(_HFCache):
         self._seen_tokens = 0
         self.defer_prefill_quantization = False
         self.max_cache_length = max_cache_length
+        # routing switches, read once per cache (i.e. once per generate() call), not per layer and token:
+        # MUZERO_DISABLE_FUSED_DECODE=1 -> dequantized K/V + stock attention; MUZERO_DISABLE_DECODE_STEP=1 ->
+        # fused attention, but append / flush / attention as separate calls
+        self.fused_decode = os.environ.get("MUZERO_DISABLE_FUSED_DECODE", "0") != "1"
+        self.fused_step = self.fused_decode and os.environ.get("MUZERO_DISABLE_DECODE_STEP", "0") != "1"
         if _HFCache is object:
             self.layers = []
             self.layer_class_to_replicate = None
@@ -300,8 +305,8 @@ def _wrap_attention_forward(module, cls_name: str, qk_norm: bool) -> None:
         if cache.defer_prefill_quantization and single:
             cache.finalize_prefill_quantization()
             cache.defer_prefill_quantization = False
-        fused = single and os.environ.get("MUZERO_DISABLE_FUSED_DECODE", "0") != "1"
-        if fused and os.environ.get("MUZERO_DISABLE_DECODE_STEP", "0") != "1" and self.layer_idx < len(cache.layers):
+        fused = single and cache.fused_decode
+        if fused and cache.fused_step and self.layer_idx < len(cache.layers):
             # steady-state decode: append, flush when due and attention in one call into the library
             if self.layer_idx == 0:
                 cache._seen_tokens += 1

@@ -145,6 +145,44 @@ def test_crop_reorder_offload(oracle):
     assert layer.get_seq_length() == 100 and torch.equal(layer.keys, full_k[[2, 0], :, :100])
 
 
+def test_batch_select_with_empty_residual_window(oracle):
+    """residual_length=0: right after a flush the window holds no token; reindexing the batch must still
+    carry it along, and decoding must go on with the new batch."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
+    k, v, q = oracle.synth_kv(3, 2, 257, 128, 8, seed=8)
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(residual_length=0))
+    layer.update(k[:, :, :256].cuda().contiguous(), v[:, :, :256].cuda().contiguous(), {"materialize_full_kv": False})
+    assert layer.keys.shape[2] == 0 and layer._key_group_count == 4
+    layer.batch_select_indices(torch.tensor([2, 0], device="cuda"))
+    assert layer.keys.shape[0] == 2 and layer._packed_key_q.shape[0] == 2
+    layer.update(k[[2, 0], :, 256:257].cuda(), v[[2, 0], :, 256:257].cuda(), {"materialize_full_kv": False})
+    ref = oracle.OracleCacheLayer(bits=4, group=64, residual=0)
+    ref.append(k[[2, 0], :, :256].contiguous(), v[[2, 0], :, :256].contiguous())
+    ref.append(k[[2, 0], :, 256:257].contiguous(), v[[2, 0], :, 256:257].contiguous())
+    want = oracle.decode_attention_oracle(q[[2, 0]], ref, 0.09, 4, compute_dtype=torch.float32)
+    got = decode_attention(layer, q[[2, 0]].cuda(), 0.09, out_dtype=torch.float32)
+    assert (got.cpu() - want).abs().max().item() <= 2e-3
+
+
+def test_first_block_with_unlike_key_value_strides(oracle):
+    """B=1, KVH=1: size-1 dimensions make strides ambiguous, so the keys (fresh from RoPE, contiguous) and the
+    values (a transposed view) of the first block can disagree in layout; the block is then copied."""
+    import muzero_b200 as mz
+    k, v, _ = oracle.synth_kv(1, 1, 300, 128, 4, seed=12)
+    kc = k.cuda().contiguous()
+    vc = v.cuda().transpose(1, 2).contiguous().transpose(1, 2)
+    if vc.stride() == kc.stride():      # make the two layouts differ for sure: a batch stride no other size-1 view has
+        vc = vc.as_strided(vc.shape, (vc.stride(0) * 3, vc.stride(1), vc.stride(2), 1))
+    assert vc.stride() != kc.stride()
+    want = mz.MuZeroCacheLayer(mz.MuZeroConfig())
+    want.update(kc, v.cuda().contiguous(), {"materialize_full_kv": False})
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig())
+    layer.update(kc, vc, {"materialize_full_kv": False})
+    assert torch.equal(layer._packed_value_q, want._packed_value_q) and torch.equal(layer._packed_key_q, want._packed_key_q)
+    assert torch.equal(layer.values, want.values) and torch.equal(layer.keys, want.keys)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("by_group,bits", [(True, 4), (False, 4), (True, 2)])
 def test_decode_step_equals_update_then_attention(oracle, by_group, bits):
@@ -162,6 +200,8 @@ def test_decode_step_equals_update_then_attention(oracle, by_group, bits):
     a, b = mz.MuZeroCacheLayer(mz.MuZeroConfig(**cfg)), mz.MuZeroCacheLayer(mz.MuZeroConfig(**cfg))
     for layer in (a, b):
         layer.update(k[:, :, :300].contiguous(), v[:, :, :300].contiguous(), {"materialize_full_kv": False})
+    ref = oracle.OracleCacheLayer(bits=bits, group=64, residual=128, flush_by_group=by_group)
+    ref.append(k[:, :, :300].cpu().contiguous(), v[:, :, :300].cpu().contiguous())
     fast = 0
     for i in range(steps):
         kn, vn = k[:, :, 300 + i:301 + i], v[:, :, 300 + i:301 + i]
@@ -171,6 +211,11 @@ def test_decode_step_equals_update_then_attention(oracle, by_group, bits):
         got = b.decode_step(kn, vn, qs[i], 0.09)
         fast += int(b._res_start >= before)
         assert torch.equal(got, want), i
+        ref.append(kn.cpu().contiguous(), vn.cpu().contiguous())
+        if i % 97 == 0 or i == steps - 1:      # the one-call step against the CPU oracle, directly
+            exact = oracle.decode_attention_oracle(qs[i].cpu(), ref, 0.09, 4, compute_dtype=torch.float32)
+            err = (got.float().cpu() - exact).abs()
+            assert bool((err <= 2e-3 + exact.abs() * 2.0 ** -8).all()), (i, err.max().item())
         assert (b._key_group_count, b._value_storage_len, b.keys.shape[2], b.cumulative_length) == \
                (a._key_group_count, a._value_storage_len, a.keys.shape[2], a.cumulative_length), i
     assert torch.equal(a._packed_key_q, b._packed_key_q) and torch.equal(a._packed_value_q, b._packed_value_q)

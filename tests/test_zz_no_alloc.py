@@ -7,7 +7,8 @@ allocator.  For them the library keeps the scratch of
 the decode attention in a static 8 MiB device array.  This test drives the entry point through
 the C ABI, twice in a row on different inputs (the array is shared and keeps old contents),
 and checks each result against the ordinary entry point (same kernels, so the tolerance the
-other attention tests use, 2e-3, is met with room to spare).  It lives in a file that pytest
+other attention tests use, 2e-3, is met with room to spare) and against the CPU oracle (the
+reference's attention evaluated in fp32, same tolerance).  It lives in a file that pytest
 collects last, so that a run that stops at the first failure has already run everything else.
 """
 import ctypes
@@ -26,6 +27,9 @@ def _layer(orc, seed, bits, batch, seq):
     k, v, q = orc.synth_kv(batch, 2, seq, 128, 8, seed=seed)
     layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=64, residual_length=128))
     layer.update(k.cuda(), v.cuda(), {"materialize_full_kv": False})
+    ref = orc.OracleCacheLayer(bits=bits, group=64, residual=128)
+    ref.append(k, v)
+    layer.oracle_output = orc.decode_attention_oracle(q, ref, 0.088, 4, compute_dtype=torch.float32)
     return layer, q.cuda()
 
 
@@ -49,9 +53,12 @@ def test_static_scratch_matches_workspace_variant_twice():
         got = _call("mz_decode_attention_static", layer, q, 0.088)
         assert torch.isfinite(got).all()
         assert (got - want).abs().max().item() <= TOL
+        assert (got.cpu() - layer.oracle_output).abs().max().item() <= TOL
     # and once more on the first case, after the array was reused by the second
     layer, q = cases[0]
-    assert (_call("mz_decode_attention_static", layer, q, 0.088) - _call("mz_decode_attention", layer, q, 0.088)).abs().max().item() <= TOL
+    again = _call("mz_decode_attention_static", layer, q, 0.088)
+    assert (again - _call("mz_decode_attention", layer, q, 0.088)).abs().max().item() <= TOL
+    assert (again.cpu() - layer.oracle_output).abs().max().item() <= TOL
 
 
 def test_static_scratch_rejects_what_it_cannot_serve():
