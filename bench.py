@@ -39,10 +39,21 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 LAYERS, BATCH, KVH, QH, CTX, RES, D, GROUP = 36, 64, 8, 32, 4096, 128, 128, 64
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_tiles_kernel launch at 4 bits, per sequence, from the
-# ncu capture summarised in profiles/decode_tiles_4bit_b32.md (batch 32: 168.13 MB + 4.04 MB); traffic is
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_mma_kernel launch at 4 bits, per sequence, from the
+# ncu capture summarised in profiles/decode_mma_4bit_b32.md (batch 32: 168.20 MB + 4.27 MB); traffic is
 # proportional to the batch, so a batch-64 launch is twice the captured one.
-NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_129_792 + 4_042_240) / 32
+NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_197_376 + 4_273_152) / 32
+METRIC = ("decode tokens/sec of the KV-cache hot path (append + flush + quantized decode attention, 36 layers, "
+          "batch 64/GPU, ctx 4096+128)")
+
+
+def workload_config(bits: int, layers: int, batch: int, world: int, context: int) -> dict:
+    """The `config` object both arms print: same keys, same values."""
+    return {"workload": f"BASELINE config 1: standalone quantized decode attention, Qwen3-8B attention shape, {layers} layers/step",
+            "bits": bits, "group": GROUP, "batch_per_gpu": batch, "global_batch": batch * world, "context": context,
+            "residual_length": RES, "kv_heads": KVH, "q_heads": QH, "head_dim": D,
+            "parallelism": f"batch-sharded x{world}, no collective",
+            "l2_policy": f"inputs larger than L2: {layers} distinct layer caches walked per step"}
 
 
 def algorithmic_bytes(bits: int, batch=BATCH, sq=CTX, res=RES, meta=2, elem=2, group=GROUP) -> int:
@@ -100,21 +111,76 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_layers(bits: int, device: torch.device, layers: int, batch: int, seed: int, ctx: int = CTX, group: int = GROUP):
-    """`layers` caches holding `ctx` quantized + RES residual tokens each (values drawn on the device)."""
+def build_layers(bits: int, device: torch.device, layers: int, batch: int, seed: int, ctx: int = CTX, group: int = GROUP,
+                 keep: list | None = None):
+    """`layers` caches holding `ctx` quantized + RES residual tokens each (values drawn on the device).
+    `keep`: receives host copies of sequence 0's K/V of the first cache (for the parity check)."""
     import muzero_b200 as mz
     gen = torch.Generator(device=device).manual_seed(seed)
     chan = torch.exp(torch.randn(D, device=device, generator=gen))
     out = []
-    for _ in range(layers):
+    for li in range(layers):
         layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=group, residual_length=RES))
         layer.max_cache_length = ctx + RES + 1024
         k = (torch.randn(batch, KVH, ctx + RES, D, device=device, generator=gen) * chan).to(torch.bfloat16)
         v = torch.randn(batch, KVH, ctx + RES, D, device=device, generator=gen).to(torch.bfloat16)
         layer.update(k, v, {"materialize_full_kv": False})
+        if li == 0 and keep is not None:
+            keep.extend([k[:1].cpu(), v[:1].cpu()])
         del k, v
         out.append(layer)
     return out
+
+
+def parity_check(layer, q: torch.Tensor, kept: list, bits: int) -> dict:
+    """One fused decode-attention call of the benched shape against the CPU oracle on sequence 0 (outside any
+    timed region): same bf16 K/V bits, same query, 2e-3 on the fp32 output, as in the parity tests."""
+    import importlib.util
+    from muzero_b200.cache.attention import decode_attention
+    spec = importlib.util.spec_from_file_location("mz_oracle", os.path.join(ROOT, "oracle", "mz_oracle.py"))
+    orc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(orc)
+    ref = orc.OracleCacheLayer(bits=bits, group=GROUP, residual=RES)
+    ref.append(kept[0], kept[1])
+    want = orc.decode_attention_oracle(q[:1].cpu(), ref, D ** -0.5, QH // KVH, compute_dtype=torch.float32)
+    got = decode_attention(layer, q, D ** -0.5, out_dtype=torch.float32)[:1].cpu()
+    err = (got - want).abs().max().item()
+    codes_equal = bool(torch.equal(layer._packed_key_q[:1].cpu(), ref.packed_k) and torch.equal(layer._packed_value_q[:1].cpu(), ref.packed_v))
+    if err > 2e-3 or not codes_equal:
+        raise RuntimeError(f"parity check failed: attention max-abs error {err}, codes equal: {codes_equal}")
+    return {"against": "CPU oracle, sequence 0 of layer 0, full batch launch", "attention_max_abs_err": err, "tolerance": 2e-3,
+            "codes_bit_exact": codes_equal}
+
+
+def time_attention(bits: int, device, batch: int, ctx: int, layers: int, steps: int = 12, warmup: int = 3) -> dict:
+    """Device time of one fused decode-attention call (main + merge kernel) on `layers` distinct caches (larger
+    than L2 together), CUDA events on the launch stream."""
+    from muzero_b200.cache.attention import build_decode_args
+    from muzero_b200.kernels.loader import load_mu_zero_cuda_extension
+    from muzero_b200.kernels._cabi import stream_ptr
+    caches = build_layers(bits, device, layers, batch, seed=4321, ctx=ctx)
+    q = torch.randn(batch, QH, 1, D, device=device).to(torch.bfloat16)
+    outs = [torch.empty(batch, 1, QH, D, dtype=torch.bfloat16, device=device) for _ in caches]
+    cargs = [build_decode_args(l, q, D ** -0.5, None, o) for l, o in zip(caches, outs)]
+    lib, st = load_mu_zero_cuda_extension(), stream_ptr(device)
+    for _ in range(warmup):
+        for a in cargs:
+            lib.mz_decode_attention(ctypes.byref(a), st)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        for a in cargs:
+            lib.mz_decode_attention(ctypes.byref(a), st)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (steps * len(cargs))
+    abytes = algorithmic_bytes(bits, batch=batch, sq=ctx)
+    peak, _ = measured_peak_gbs()
+    del caches, cargs
+    torch.cuda.empty_cache()
+    return {"bits": bits, "batch": batch, "context": ctx + RES, "us_per_launch": us, "bytes_per_launch": abytes,
+            "achieved": abytes / us / 1e3, "frac": abytes / us / 1e3 / peak, "distinct_caches": layers}
 
 
 class CabiSession:
@@ -176,9 +242,11 @@ def run_ours(args) -> dict:
         return float(t.item())
 
     bits, L, B = args.bits, args.layers, args.batch
-    layers = build_layers(bits, device, L, B, seed=1234 + rank)
+    kept: list = []
+    layers = build_layers(bits, device, L, B, seed=1234 + rank, keep=kept if rank == 0 else None)
     gen = torch.Generator(device=device).manual_seed(99 + rank)
     q = torch.randn(B, QH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+    parity = parity_check(layers[0], q, kept, bits) if rank == 0 else None
     k_new = torch.randn(B, KVH, 1, D, device=device, generator=gen).to(torch.bfloat16)
     v_new = torch.randn(B, KVH, 1, D, device=device, generator=gen).to(torch.bfloat16)
 
@@ -256,8 +324,21 @@ def run_ours(args) -> dict:
     peak, peak_kind = measured_peak_gbs()
     abytes = algorithmic_bytes(bits, batch=B)
     achieved = abytes / (attn_us * 1e-6) / 1e9
+    # ---------------- after the timed regions: the other points of the metric (rank 0's GPU; every rank measures so
+    # that the GPUs stay in step): 2-bit codes at the same shape, and longer contexts at batch 64
+    extra = {}
+    if not args.no_sweep:
+        del sess, cache
+        layers.clear()
+        torch.cuda.empty_cache()
+        other = 2 if bits == 4 else 4
+        extra[f"roofline_{other}bit"] = time_attention(other, device, B, CTX, layers=4)
+        extra["ctx_sweep"] = [time_attention(bits, device, B, c, layers=2, steps=6) for c in (8192, 32768)]
+        barrier()
+        if world > 1:
+            extra["kv_split"] = [kv_split_point(b_, device, rank, world, dist) for b_ in (4, 2)]
     result = {
-        "metric": "decode tokens/sec of the KV-cache hot path (append + flush + quantized decode attention, 36 layers, batch 64/GPU, ctx 4096+128)",
+        "metric": METRIC,
         "value": world * B * args.steps / (ms_total * 1e-3),
         "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -265,19 +346,17 @@ def run_ours(args) -> dict:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": f"u{bits} codes, fp16 metadata, bf16 residual, f32 accumulation",
         "data": "synthetic",
-        "config": {"workload": f"BASELINE config 1: standalone quantized decode attention, Qwen3-8B attention shape, {L} layers/step",
-                   "bits": bits, "group": GROUP, "batch_per_gpu": B, "global_batch": B * world, "context": ctx_now,
-                   "residual_length": RES, "kv_heads": KVH, "q_heads": QH, "head_dim": D,
-                   "parallelism": f"batch-sharded x{world}, no collective",
-                   "l2_policy": f"inputs larger than L2: {L} distinct layer caches walked per step"},
+        "config": workload_config(bits, L, B, world, ctx_now),
         "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_DRAM_BYTES_PER_SEQ_4BIT * B if bits == 4 else None, "peak_kind": peak_kind, "kernel": "decode_tiles_kernel + combine_tiles_kernel",
+                     "traffic": NCU_DRAM_BYTES_PER_SEQ_4BIT * B if bits == 4 else None, "peak_kind": peak_kind, "kernel": "decode_mma_kernel + combine_tiles_kernel",
                      "bytes_per_launch": abytes, "us_per_launch": attn_us},
         "clocks": clocks,
+        "parity_check": parity,
     }
+    result.update(extra)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(bits, seconds=12.0)
     if world > 1:
@@ -317,13 +396,66 @@ def run_attention_only(args) -> dict:
             "bytes_per_call": abytes, "achieved_gbs": abytes / us / 1e3, "frac_of_peak": abytes / us / 1e3 / peak, "peak_kind": kind}
 
 
-def run_kv_split(args) -> dict:
-    """Secondary workload (BASELINE config 4): one very long context split over the ranks' GPUs.  Each rank
-    holds a contiguous slice of `--context` quantized tokens (the last one also the residual window), computes
-    its partial (m, l, acc), the triples are all-gathered (NCCL) and merged on every rank.  Timed with CUDA
-    events around the whole call (partial + all-gather + merge), max over ranks."""
-    import torch.distributed as dist
+def kv_split_point(bits: int, device, rank: int, world: int, dist, batch: int = 8, context: int = 131072, layers: int = 2,
+                   steps: int = 6, warmup: int = 2, group: int = GROUP) -> dict:
+    """One point of the KV-sequence split (BASELINE config 4 shape): one very long context cut over the ranks' GPUs.
+    Each rank holds a contiguous slice of `context` quantized tokens (the last one also the residual window),
+    computes its partial (m, l, acc); the triples are all-gathered (NCCL) and merged on every rank.  CUDA events
+    around whole calls (partial + all-gather + merge), max over ranks."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention
     from muzero_b200.distributed import kv_split_decode_attention, kv_split_ranges
+    lo, hi = kv_split_ranges(context, world, group)[rank]
+    res = RES if rank == world - 1 else 0
+    gen = torch.Generator(device=device).manual_seed(77)            # same stream on every rank: identical q
+    q = torch.randn(batch, QH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+    gen.manual_seed(1000 + rank)
+    caches = []
+    for _ in range(layers):
+        layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=group, residual_length=res,
+                                                    alpha_key=2.0, alpha_value=2.0))
+        n = hi - lo + res
+        k = torch.randn(batch, KVH, n, D, device=device, generator=gen).to(torch.bfloat16)
+        v = torch.randn(batch, KVH, n, D, device=device, generator=gen).to(torch.bfloat16)
+        layer.update(k, v, {"materialize_full_kv": False})
+        del k, v
+        caches.append(layer)
+
+    def one_round():
+        for layer in caches:
+            if world > 1:
+                kv_split_decode_attention(layer, q, D ** -0.5)
+            else:
+                decode_attention(layer, q, D ** -0.5)
+
+    for _ in range(warmup):
+        one_round()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one_round()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    us = ms.item() * 1e3 / (steps * len(caches))
+    abytes = algorithmic_bytes(bits, batch=batch, sq=context, group=group)
+    peak, kind = measured_peak_gbs()
+    del caches
+    torch.cuda.empty_cache()
+    return {"mode": "kv-split", "n_gpus": world, "bits": bits, "group": group, "batch": batch, "context": context,
+            "layers": layers, "us_per_call": us, "bytes_per_call_all_ranks": abytes,
+            "achieved_gbs_all_ranks": abytes / us / 1e3, "frac_of_peak_per_gpu": abytes / us / 1e3 / peak / world,
+            "collective": "all_gather of (m, l, acc) partials, then a local merge kernel" if world > 1 else "none", "peak_kind": kind}
+
+
+def run_kv_split(args) -> dict:
+    """Secondary workload on its own: `bench.py --kv-split [--gpus N]` (see kv_split_point)."""
+    import torch.distributed as dist
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     device = torch.device("cuda", local)
@@ -331,53 +463,11 @@ def run_kv_split(args) -> dict:
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
-    lo, hi = kv_split_ranges(args.context, world, args.group)[rank]
-    res = RES if rank == world - 1 else 0
-    import muzero_b200 as mz
-    gen = torch.Generator(device=device).manual_seed(77)            # same stream on every rank: identical q
-    q = torch.randn(args.batch, QH, 1, D, device=device, generator=gen).to(torch.bfloat16)
-    gen.manual_seed(1000 + rank)
-    layers = []
-    for _ in range(args.layers):
-        layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=args.bits, q_group_size=args.group, residual_length=res,
-                                                    alpha_key=2.0, alpha_value=2.0))
-        n = hi - lo + res
-        k = torch.randn(args.batch, KVH, n, D, device=device, generator=gen).to(torch.bfloat16)
-        v = torch.randn(args.batch, KVH, n, D, device=device, generator=gen).to(torch.bfloat16)
-        layer.update(k, v, {"materialize_full_kv": False})
-        del k, v
-        layers.append(layer)
-
-    def one_round():
-        for layer in layers:
-            if world > 1:
-                kv_split_decode_attention(layer, q, D ** -0.5)
-            else:
-                from muzero_b200.cache.attention import decode_attention
-                decode_attention(layer, q, D ** -0.5)
-
-    for _ in range(args.warmup):
-        one_round()
-    torch.cuda.synchronize()
+    out = kv_split_point(args.bits, device, rank, world, dist, batch=args.batch, context=args.context, layers=args.layers,
+                         steps=args.steps, warmup=args.warmup, group=args.group)
     if world > 1:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        one_round()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         dist.destroy_process_group()
-    us = ms.item() * 1e3 / (args.steps * len(layers))
-    abytes = algorithmic_bytes(args.bits, batch=args.batch, sq=args.context, group=args.group)
-    peak, kind = measured_peak_gbs()
-    return {"mode": "kv-split", "n_gpus": world, "bits": args.bits, "group": args.group, "batch": args.batch,
-            "context": args.context, "layers": args.layers, "us_per_call": us, "bytes_per_call_all_ranks": abytes,
-            "achieved_gbs_all_ranks": abytes / us / 1e3, "frac_of_peak_per_gpu": abytes / us / 1e3 / peak / world,
-            "peak_kind": kind} if rank == 0 else {}
+    return out if rank == 0 else {}
 
 
 def run_generate(args) -> dict:
@@ -418,15 +508,37 @@ def run_generate(args) -> dict:
         kwargs.update(cache_implementation=f"mu_zero_{args.bits}bit",
                       cache_config={"q_group_size": GROUP, "residual_length": RES, "backend": "cuda"})
     clock = Clock()
+    grabbed = []          # the cache object generate() builds, for the cache-bytes columns
+    if args.cache == "mu_zero":
+        from muzero_b200.integrations import transformers_patch as tp
+        real_init = tp.MuZeroCache.__init__
+        def grabbing_init(self, *a, **kw):
+            real_init(self, *a, **kw)
+            grabbed.append(self)
+        tp.MuZeroCache.__init__ = grabbing_init
     muzero.reset_mu_zero_decode_stats()
     torch.cuda.reset_peak_memory_stats()
     with torch.no_grad():
         out = model.generate(input_ids=ids, attention_mask=torch.ones_like(ids), streamer=clock, **kwargs)
+    if args.cache == "mu_zero":
+        tp.MuZeroCache.__init__ = real_init
     # stamps[0] = prompt echo, stamps[1] = first new token (end of prefill); decode = the rest
     t = clock.stamps
     decode_s = t[-1] - t[1]
     steps = len(t) - 2
-    return {"mode": "generate", "cache": args.cache, "bits": args.bits, "layers": args.layers, "batch": args.batch,
+    cache_mb = {}
+    if args.cache == "mu_zero" and grabbed:
+        # the reference's rule (benchmarks/bench_throughput.py:199-224): packed codes, metadata, residual buffers
+        mb = lambda x: 0.0 if x is None else x.numel() * x.element_size() / 1024 ** 2
+        packed = meta = resid = 0.0
+        for layer in grabbed[0].layers:
+            packed += mb(layer._packed_key_q) + mb(layer._packed_value_q)
+            meta += sum(mb(getattr(layer, a)) for a in ("_key_mn", "_key_scale", "_value_mn", "_value_scale"))
+            resid += mb(layer._key_buffer if layer._key_buffer is not None else layer.keys)
+            resid += mb(layer._value_buffer if layer._value_buffer is not None else layer.values)
+        cache_mb = {"cache_packed_mb": packed, "cache_meta_mb": meta, "cache_residual_mb": resid,
+                    "cache_total_mb": packed + meta + resid}
+    return {**cache_mb, "mode": "generate", "cache": args.cache, "bits": args.bits, "layers": args.layers, "batch": args.batch,
             "context": args.context, "new_tokens": int(out.shape[1] - ids.shape[1]),
             "prefill_s": t[1] - t[0], "decode_tokens_per_s": args.batch * steps / decode_s, "ms_per_decode_step": 1e3 * decode_s / steps,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30, "decode_stats": muzero.get_mu_zero_decode_stats()}
@@ -462,20 +574,25 @@ def cpu_baseline(bits: int, seconds: float) -> dict:
 
 
 def run_reference(args) -> dict:
+    """The reference arm: the reference's CPU (torch backend) implementation of the path, as restated in oracle/, on
+    the host cores, on a bounded sample of the same workload.  Under a multi-rank launch rank 0 alone runs it (a CPU
+    arm does not scale with the GPU count); it uses every host core (the launcher pins OMP_NUM_THREADS=1, which is undone)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return {}
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     t0 = time.perf_counter()
     base = cpu_baseline(args.bits, seconds=max(10.0, min(90.0, 2.0 * args.steps)))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     return {
         "impl": "reference",
-        "metric": "decode tokens/sec of the KV-cache hot path (append + flush + quantized decode attention, 36 layers, batch 64/GPU, ctx 4096+128)",
+        "metric": METRIC,
         "value": base["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * BATCH / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16 torch CPU ops (the reference's torch backend restated)", "data": "synthetic",
-        "config": {"workload": f"BASELINE config 1: standalone quantized decode attention, Qwen3-8B attention shape, {LAYERS} layers/step",
-                   "bits": args.bits, "group": GROUP, "batch_per_gpu": BATCH, "context": CTX + RES},
+        "dtype": f"u{args.bits} codes, fp16 metadata, bf16 residual (torch CPU ops in bf16, the reference's torch backend)",
+        "data": "synthetic",
+        "config": workload_config(args.bits, LAYERS, BATCH, world, CTX + RES + args.warmup + args.steps),
+        "extrapolated": True,      # value and ms_per_step are scaled from the sample named in cpu_baseline.sample
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
@@ -492,6 +609,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the measurements after the timed regions (2-bit, longer contexts, KV split)")
     ap.add_argument("--attention-only", action="store_true", help="small profiling case: only the fused attention calls")
     ap.add_argument("--kv-split", action="store_true", help="secondary workload: one long context split over the GPUs of the run")
     ap.add_argument("--generate", action="store_true", help="secondary workload: HF generate() on a Qwen3-8B shaped model")

@@ -250,6 +250,17 @@ int mz_lse_merge(const float* m, const float* l, const float* acc, int n_parts,
                  long long rows, int head_dim, void* out, int out_dtype, void* stream);
 
 /*
+ * The same two steps with one packed record per (batch, head) row, records[B*H][D+2] =
+ * {acc[D], m, l} (fp32): the partial call writes it, the merge reads n_parts of them laid out
+ * [n_parts][B*H][D+2].  This is the unit that crosses GPUs when the KV sequence is split: one
+ * contiguous buffer per rank for the all-gather, no re-packing on either side.
+ * Replaces: the same reference code as mz_decode_attention_partial / mz_lse_merge.
+ */
+int mz_decode_attention_partial_packed(const mz_decode_args* args, float* records, void* stream);
+int mz_lse_merge_packed(const float* records, int n_parts, long long rows, int head_dim, void* out,
+                        int out_dtype, void* stream);
+
+/*
  * Stand-alone halves of the attention, kept for callers of the reference's
  * two-kernel path (the fused call above is the fast one):
  *   mz_qk_logits: out[B,H,k_groups*G] (out_dtype) = scaling * <q[b,h,:], K^[b,h/gqa,t,:]>

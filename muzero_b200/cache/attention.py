@@ -174,6 +174,33 @@ def decode_attention_partial(layer, query: torch.Tensor, scaling: float, attenti
     return m, l, acc
 
 
+def decode_attention_partial_packed(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor] = None,
+                                    *, splits: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same triple as one packed fp32 record per row: ``[B,H,D+2]`` = ``{acc[D], m, l}`` (the unit that is
+    all-gathered when the KV sequence is split over GPUs).  ``out``: write into this buffer."""
+    b, h, _, d = query.shape
+    rec = out if out is not None else torch.empty((b, h, d + 2), dtype=torch.float32, device=query.device)
+    args = build_decode_args(layer, query, scaling, attention_mask, None, splits=splits)
+    with torch.cuda.device(query.device):
+        check(load_mu_zero_cuda_extension().mz_decode_attention_partial_packed(
+            ctypes.byref(args), rec.data_ptr(), stream_ptr(query.device)), "mz_decode_attention_partial_packed")
+    return rec
+
+
+def lse_merge_packed(records: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Merges packed records stacked on dim 0 (``[P,B,H,D+2]``, contiguous) -> normalised ``[B,1,H,D]``."""
+    p, b, h, dd = records.shape
+    d = dd - 2
+    if not records.is_contiguous():
+        records = records.contiguous()
+    out = torch.empty((b, 1, h, d), dtype=out_dtype, device=records.device)
+    with torch.cuda.device(records.device):
+        check(load_mu_zero_cuda_extension().mz_lse_merge_packed(records.data_ptr(), p, b * h, d, out.data_ptr(),
+                                                                dtype_code(out_dtype), stream_ptr(records.device)),
+              "mz_lse_merge_packed")
+    return out
+
+
 def lse_merge(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """Merges partial triples stacked on dim 0 ([P,B,H], [P,B,H], [P,B,H,D]) -> [B,1,H,D]."""
     p, b, h, d = acc.shape

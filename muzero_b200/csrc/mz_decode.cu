@@ -8,31 +8,35 @@
 
 namespace {
 
+// Strided views of partial triples: record (row, part) has its m / l at m[row*m_row + part*m_part] and its
+// acc[D] at acc + row*a_row + part*a_part.
+struct PartialView {
+  const float* m; const float* l; const float* acc;
+  long long m_row, m_part, a_row, a_part;
+};
+
 // out[row, :] = sum_p acc[p,row,:] * exp(m[p,row] - m*) (/ sum_p l[p,row] * exp(m[p,row] - m*) when normalising)
-__global__ void lse_combine_kernel(const float* __restrict__ m, const float* __restrict__ l, const float* __restrict__ acc,
-                                   int n_parts, long long row_stride, long long part_stride, int D,
-                                   void* __restrict__ out, int out_dt, float* __restrict__ out_m, float* __restrict__ out_l,
-                                   float* __restrict__ out_acc) {
+__global__ void lse_combine_kernel(const PartialView v, int n_parts, int D, const MzDecodeOut o) {
   const long long row = blockIdx.x;
   float mx = -INFINITY;
-  for (int p = 0; p < n_parts; ++p) mx = fmaxf(mx, m[row * row_stride + p * part_stride]);
+  for (int p = 0; p < n_parts; ++p) mx = fmaxf(mx, v.m[row * v.m_row + p * v.m_part]);
   float lsum = 0.f;
   for (int p = 0; p < n_parts; ++p) {
-    const long long i = row * row_stride + p * part_stride;
-    const float w = (m[i] > -INFINITY) ? __expf(m[i] - mx) : 0.f;
-    lsum += l[i] * w;
+    const long long i = row * v.m_row + p * v.m_part;
+    const float w = (v.m[i] > -INFINITY) ? __expf(v.m[i] - mx) : 0.f;
+    lsum += v.l[i] * w;
   }
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float a = 0.f;
     for (int p = 0; p < n_parts; ++p) {
-      const long long i = row * row_stride + p * part_stride;
-      const float w = (m[i] > -INFINITY) ? __expf(m[i] - mx) : 0.f;
-      a = fmaf(acc[i * D + d], w, a);
+      const float mi = v.m[row * v.m_row + p * v.m_part];
+      const float w = (mi > -INFINITY) ? __expf(mi - mx) : 0.f;
+      a = fmaf(v.acc[row * v.a_row + p * v.a_part + d], w, a);
     }
-    if (out) mz_store_from_float(out, row * D + d, a / fmaxf(lsum, 1e-20f), out_dt);
-    else out_acc[row * D + d] = a;
+    if (o.out) mz_store_from_float(o.out, row * D + d, a / fmaxf(lsum, 1e-20f), o.out_dt);
+    else o.acc[row * o.acc_stride + d] = a;
   }
-  if (!out && threadIdx.x == 0) { out_m[row] = mx; out_l[row] = lsum; }
+  if (!o.out && threadIdx.x == 0) { o.m[row * o.ml_stride] = mx; o.l[row * o.ml_stride] = lsum; }
 }
 
 // SM count of the current device (cached per device index: a process may drive unlike GPUs)
@@ -144,8 +148,8 @@ int finish(const Plan& plan, const MzDecodeOut& o, cudaStream_t st) {
   if (plan.tiles) return mz_combine_tiles(p, o, st);
   const int D = p.s.head_dim;
   const int threads = D >= 128 ? 128 : ((D + 31) / 32) * 32;
-  lse_combine_kernel<<<(unsigned)(p.s.batch * p.H), threads, 0, st>>>(p.part.m, p.part.l, p.part.acc, p.splits, p.splits, 1, D, o.out,
-                                                                      o.out_dt, o.m, o.l, o.acc);
+  const PartialView v = {p.part.m, p.part.l, p.part.acc, p.splits, 1, (long long)p.splits * D, D};
+  lse_combine_kernel<<<(unsigned)(p.s.batch * p.H), threads, 0, st>>>(v, p.splits, D, o);
   MZ_LAUNCH_CHECK("lse_combine");
   return MZ_OK;
 }
@@ -170,7 +174,7 @@ int mz_decode_plan(const mz_decode_args* a, MzDecodePlan* plan) {
 int mz_decode_run_plan(const mz_decode_args* a, MzDecodePlan* plan, cudaStream_t st) {
   int rc = launch_partials(a, plan, st);
   if (rc) return rc;
-  const MzDecodeOut o = {a->out, a->out_dtype, nullptr, nullptr, nullptr};
+  const MzDecodeOut o = {a->out, a->out_dtype, nullptr, nullptr, nullptr, 0, 0};
   return finish(*plan, o, st);
 }
 
@@ -204,7 +208,7 @@ extern "C" int mz_decode_attention(const mz_decode_args* a, void* stream) {
   MZ_REQUIRE(a != nullptr && a->out != nullptr && mz_dtype_ok(a->out_dtype), "bad output");
   int rc = run_partials(a, &plan, st);
   if (rc) return rc;
-  const MzDecodeOut o = {a->out, a->out_dtype, nullptr, nullptr, nullptr};
+  const MzDecodeOut o = {a->out, a->out_dtype, nullptr, nullptr, nullptr, 0, 0};
   return finish(plan, o, st);
 }
 
@@ -214,19 +218,45 @@ extern "C" int mz_decode_attention_partial(const mz_decode_args* a, float* m, fl
   MZ_REQUIRE(m && l && acc, "NULL partial output");
   int rc = run_partials(a, &plan, st);
   if (rc) return rc;
-  const MzDecodeOut o = {nullptr, MZ_F32, m, l, acc};
+  const MzDecodeOut o = {nullptr, MZ_F32, m, l, acc, a->store.head_dim, 1};
   return finish(plan, o, st);
 }
 
-extern "C" int mz_lse_merge(const float* m, const float* l, const float* acc, int n_parts, long long rows, int head_dim, void* out,
-                            int out_dtype, void* stream) {
-  MZ_REQUIRE(m && l && acc && out, "NULL pointer");
+extern "C" int mz_decode_attention_partial_packed(const mz_decode_args* a, float* records, void* stream) {
+  Plan plan;
+  cudaStream_t st = (cudaStream_t)stream;
+  MZ_REQUIRE(records != nullptr, "NULL partial output");
+  int rc = run_partials(a, &plan, st);
+  if (rc) return rc;
+  const int D = a->store.head_dim;
+  const MzDecodeOut o = {nullptr, MZ_F32, records + D, records + D + 1, records, D + 2, D + 2};
+  return finish(plan, o, st);
+}
+
+namespace {
+int merge_launch(const PartialView& v, int n_parts, long long rows, int head_dim, void* out, int out_dtype, void* stream) {
+  MZ_REQUIRE(v.m && v.l && v.acc && out, "NULL pointer");
   MZ_REQUIRE(n_parts > 0 && rows > 0 && head_dim > 0, "bad shape");
   MZ_REQUIRE(mz_dtype_ok(out_dtype), "bad out_dtype");
   MZ_REQUIRE(rows < (1LL << 31), "too many rows");
   const int threads = head_dim >= 128 ? 128 : ((head_dim + 31) / 32) * 32;
-  lse_combine_kernel<<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(m, l, acc, n_parts, 1, rows, head_dim, out, out_dtype, nullptr,
-                                                                           nullptr, nullptr);
+  const MzDecodeOut o = {out, out_dtype, nullptr, nullptr, nullptr, 0, 0};
+  lse_combine_kernel<<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(v, n_parts, head_dim, o);
   MZ_LAUNCH_CHECK("lse_merge");
   return MZ_OK;
+}
+}  // namespace
+
+extern "C" int mz_lse_merge(const float* m, const float* l, const float* acc, int n_parts, long long rows, int head_dim, void* out,
+                            int out_dtype, void* stream) {
+  const PartialView v = {m, l, acc, 1, rows, head_dim, rows * head_dim};
+  return merge_launch(v, n_parts, rows, head_dim, out, out_dtype, stream);
+}
+
+extern "C" int mz_lse_merge_packed(const float* records, int n_parts, long long rows, int head_dim, void* out, int out_dtype,
+                                   void* stream) {
+  MZ_REQUIRE(records != nullptr, "NULL pointer");
+  const long long rec = head_dim + 2;
+  const PartialView v = {records + head_dim, records + head_dim + 1, records, rec, rows * rec, rec, rows * rec};
+  return merge_launch(v, n_parts, rows, head_dim, out, out_dtype, stream);
 }

@@ -68,10 +68,13 @@ struct MzDecodeParams {
   MzTilesPlan tp;
 };
 
-// where a call's result goes: normalised output, or the merged (m, l, acc) triple
+// where a call's result goes: normalised output, or the merged (m, l, acc) triple.  The triple is addressed
+// with strides so that it can be written as separate arrays (acc_stride = D, ml_stride = 1) or as one packed
+// record per row, [acc[D], m, l] (acc_stride = ml_stride = D + 2, m = acc + D, l = acc + D + 1).
 struct MzDecodeOut {
   void* out; int out_dt;
   float* m; float* l; float* acc;
+  long long acc_stride, ml_stride;
 };
 
 // A validated call: which kernel runs, its parameters, the partial records and scratch bytes it needs.

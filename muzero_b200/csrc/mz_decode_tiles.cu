@@ -624,8 +624,8 @@ __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams
     const long long row = (long long)pair * gqa + h;
     if (o.out) mz_store_from_float(o.out, row * D + d, a / fmaxf(lsum, 1e-20f), o.out_dt);
     else {
-      o.acc[row * D + d] = a;
-      if (d == 0) { o.m[row] = mx; o.l[row] = lsum; }
+      o.acc[row * o.acc_stride + d] = a;
+      if (d == 0) { o.m[row * o.ml_stride] = mx; o.l[row * o.ml_stride] = lsum; }
     }
   }
 }

@@ -42,32 +42,47 @@ def kv_split_ranges(total_tokens: int, world: int, group: int) -> list[tuple[int
     return out
 
 
-def gather_partials(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor,
-                    group: Optional[dist.ProcessGroup] = None):
-    """All-gathers one rank's (m[B,H], l[B,H], acc[B,H,D]) into stacked [world, ...] tensors.
+def pack_partial(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor) -> torch.Tensor:
+    """(m[B,H], l[B,H], acc[B,H,D]) -> one record tensor [B,H,D+2] = {acc, m, l}."""
+    return torch.cat([acc, m.unsqueeze(-1), l.unsqueeze(-1)], dim=-1).contiguous()
 
-    The three tensors travel as one buffer [B,H,D+2] so that a decode step costs one collective."""
+
+def unpack_partials(records: torch.Tensor):
+    """[...,D+2] records -> views (m, l, acc)."""
+    d = records.shape[-1] - 2
+    return records[..., d], records[..., d + 1], records[..., :d]
+
+
+_gather_buffers: dict = {}
+
+
+def gather_records(record: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gathers one rank's packed record [B,H,D+2] into [world,B,H,D+2]: the one collective of a decode
+    step, into a buffer kept per (device, shape, world)."""
     world = dist.get_world_size(group)
-    packed = torch.cat([acc, m.unsqueeze(-1), l.unsqueeze(-1)], dim=-1).contiguous()
-    flat = torch.empty((world * packed.shape[0], *packed.shape[1:]), dtype=packed.dtype, device=packed.device)
-    dist.all_gather_into_tensor(flat, packed, group=group)
-    out = flat.view(world, *packed.shape)
-    d = acc.shape[-1]
-    return out[..., d].contiguous(), out[..., d + 1].contiguous(), out[..., :d].contiguous()
+    key = (record.device, tuple(record.shape), world)
+    flat = _gather_buffers.get(key)
+    if flat is None:
+        flat = torch.empty((world, *record.shape), dtype=record.dtype, device=record.device)
+        _gather_buffers[key] = flat
+    # the collective sees the ranks' records concatenated along the first dimension
+    dist.all_gather_into_tensor(flat.view(world * record.shape[0], *record.shape[1:]), record, group=group)
+    return flat
 
 
 def kv_split_decode_attention(layer, query: torch.Tensor, scaling: float, *, out_dtype: Optional[torch.dtype] = None,
                               group: Optional[dist.ProcessGroup] = None,
-                              partial_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None) -> torch.Tensor:
+                              record_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None) -> torch.Tensor:
     """Decode attention when ``layer`` holds only this rank's slice of the sequence.
 
-    Every rank gets the full result [B,1,H,D].  ``partial_fn`` / ``merge_fn`` default to the CUDA
-    entry points (``mz_decode_attention_partial`` / ``mz_lse_merge``); tests of the host logic on
-    CPU ranks substitute CPU functions."""
-    if partial_fn is None or merge_fn is None:
-        from .cache.attention import decode_attention_partial, lse_merge
-        partial_fn = partial_fn or decode_attention_partial
-        merge_fn = merge_fn or lse_merge
-    m, l, acc = partial_fn(layer, query, scaling)
-    ms, ls, accs = gather_partials(m, l, acc, group)
-    return merge_fn(ms, ls, accs, out_dtype or query.dtype)
+    Every rank gets the full result [B,1,H,D].  Three launches per call: the partial kernel writes this rank's
+    packed record, NCCL all-gathers the records into local memory, the merge kernel reads them with a stride.
+    ``record_fn(layer, query, scaling) -> [B,H,D+2]`` and ``merge_fn(records[world,B,H,D+2], dtype)`` default to
+    the CUDA entry points (``mz_decode_attention_partial_packed`` / ``mz_lse_merge_packed``); tests of the host
+    logic on CPU ranks substitute CPU functions."""
+    if record_fn is None or merge_fn is None:
+        from .cache.attention import decode_attention_partial_packed, lse_merge_packed
+        record_fn = record_fn or decode_attention_partial_packed
+        merge_fn = merge_fn or lse_merge_packed
+    records = gather_records(record_fn(layer, query, scaling), group)
+    return merge_fn(records, out_dtype or query.dtype)

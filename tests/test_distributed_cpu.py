@@ -39,19 +39,20 @@ def _rank_main(rank, world, port, q_out):
     import sys
     sys.path.insert(0, ROOT)
     orc = load_oracle()
-    from muzero_b200.distributed import kv_split_decode_attention, kv_split_ranges, batch_shard
+    from muzero_b200.distributed import kv_split_decode_attention, kv_split_ranges, batch_shard, pack_partial, unpack_partials
     k, v, q = orc.synth_kv(2, 2, 512, 64, 8, seed=5)           # same on every rank
     s, e = kv_split_ranges(512, world, 64)[rank]
 
-    def partial_fn(layer, query, scaling):                       # CPU stand-in for the CUDA partial kernel
-        return orc.attention_partial_oracle(query, layer[0], layer[1], scaling, 4)
+    def record_fn(layer, query, scaling):                        # CPU stand-in for the CUDA partial kernel
+        return pack_partial(*orc.attention_partial_oracle(query, layer[0], layer[1], scaling, 4))
 
-    def merge_fn(ms, ls, accs, dtype):
+    def merge_fn(records, dtype):                                # ... and for the merge kernel
+        ms, ls, accs = unpack_partials(records)
         out = orc.lse_merge_oracle(list(ms), list(ls), list(accs))
         return out.unsqueeze(1).to(dtype)
 
     out = kv_split_decode_attention((k[:, :, s:e].float(), v[:, :, s:e].float()), q, 0.125, out_dtype=torch.float32,
-                                    partial_fn=partial_fn, merge_fn=merge_fn)
+                                    record_fn=record_fn, merge_fn=merge_fn)
     m, l, acc = orc.attention_partial_oracle(q, k.float(), v.float(), 0.125, 4)
     whole = (acc / l.unsqueeze(-1)).unsqueeze(1)
     err = (out - whole).abs().max().item()
