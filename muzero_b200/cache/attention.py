@@ -159,6 +159,58 @@ def _decode_attention_unaligned(layer, query: torch.Tensor, scaling: float, atte
     return out.reshape(b, 1, h, d).to(out_dtype)
 
 
+def decode_attention_reference_rounding(layer, query: torch.Tensor, scaling: float,
+                                        attention_mask: Optional[torch.Tensor] = None, *, key_chunk_groups: int = 32,
+                                        value_chunk_tokens: int = 256) -> torch.Tensor:
+    """Parity mode: the same attention with the rounding points of the reference's torch path.
+
+    The fused kernel keeps every intermediate in fp32.  The reference's path
+    (muzero/cache/attention.py:213-239,274-290) rounds to the model dtype after the dequantization, after
+    ``q K^T``, after the multiplication by ``scaling``, after the fp32 softmax, after every 256-token ``w V``
+    piece and after each addition of the pieces, which moves the output by up to ~0.04.  This route repeats
+    those steps on the device, op for op, with this library's bit-exact dequantizer; what still differs from
+    a CPU run of the reference is the summation order inside the matmuls.  It is a debugging aid for token
+    comparisons (``MUZERO_PARITY_MODE=1``), not a fast path."""
+    if not query.is_cuda:
+        raise MuZeroKernelError("decode attention needs CUDA tensors; this package has no CPU path")
+    g, groups = layer.q_group_size, layer._key_group_count
+    kvh = layer.keys.shape[1]
+    rep = query.shape[1] // kvh
+
+    def repeat_kv(x):
+        return x if rep == 1 else x[:, :, None].expand(x.shape[0], kvh, rep, x.shape[2], x.shape[3]).reshape(
+            x.shape[0], kvh * rep, x.shape[2], x.shape[3])
+
+    parts, cursor = [], 0
+    for sg in range(0, groups, key_chunk_groups):
+        kc = repeat_kv(layer._dequantize_key_range(sg, min(sg + key_chunk_groups, groups)))
+        lg = torch.matmul(query, kc.transpose(2, 3)) * scaling
+        if attention_mask is not None:
+            lg = lg + attention_mask[..., cursor:cursor + kc.shape[-2]]
+        parts.append(lg)
+        cursor += kc.shape[-2]
+    dk = repeat_kv(layer.keys)
+    if dk.shape[-2] > 0:
+        lg = torch.matmul(query, dk.transpose(2, 3)) * scaling
+        if attention_mask is not None:
+            lg = lg + attention_mask[..., cursor:cursor + dk.shape[-2]]
+        parts.append(lg)
+    w = torch.softmax(torch.cat(parts, dim=-1), dim=-1, dtype=torch.float32).to(query.dtype)
+    out, cursor = None, 0
+    for st in range(0, layer._value_storage_len, value_chunk_tokens):
+        vc = repeat_kv(layer._dequantize_value_range(st, min(st + value_chunk_tokens, layer._value_storage_len)))
+        piece = torch.matmul(w[..., cursor:cursor + vc.shape[-2]], vc)
+        out = piece if out is None else out + piece
+        cursor += vc.shape[-2]
+    dv = repeat_kv(layer.values)
+    if dv.shape[-2] > 0:
+        piece = torch.matmul(w[..., cursor:cursor + dv.shape[-2]], dv)
+        out = piece if out is None else out + piece
+    if out is None:
+        raise MuZeroKernelError("no tokens to attend to")
+    return out.transpose(1, 2).contiguous()
+
+
 def decode_attention_partial(layer, query: torch.Tensor, scaling: float, attention_mask: Optional[torch.Tensor] = None,
                              *, splits: int = 0):
     """Un-normalised (m[B,H], l[B,H], acc[B,H,D]) fp32 triple of this layer's tokens."""

@@ -40,12 +40,16 @@ class MuZeroCache(_HFCache):
         self.cfg = cfg
         self._seen_tokens = 0
         self.defer_prefill_quantization = False
+        self.single_shot_prefill = False      # the whole prompt arrives as one block per layer
         self.max_cache_length = max_cache_length
         # routing switches, read once per cache (i.e. once per generate() call), not per layer and token:
         # MUZERO_DISABLE_FUSED_DECODE=1 -> dequantized K/V + stock attention; MUZERO_DISABLE_DECODE_STEP=1 ->
         # fused attention, but append / flush / attention as separate calls
         self.fused_decode = os.environ.get("MUZERO_DISABLE_FUSED_DECODE", "0") != "1"
-        self.fused_step = self.fused_decode and os.environ.get("MUZERO_DISABLE_DECODE_STEP", "0") != "1"
+        # MUZERO_PARITY_MODE=1 -> decode attention with the reference's rounding points (slow, for token comparisons)
+        self.parity_mode = os.environ.get("MUZERO_PARITY_MODE", "0") == "1"
+        self.fused_step = (self.fused_decode and not self.parity_mode
+                           and os.environ.get("MUZERO_DISABLE_DECODE_STEP", "0") != "1")
         if _HFCache is object:
             self.layers = []
             self.layer_class_to_replicate = None
@@ -73,6 +77,22 @@ class MuZeroCache(_HFCache):
         kwargs = dict(cache_kwargs or {})
         kwargs.setdefault("materialize_full_kv", True)   # unknown callers get ordinary dense K/V back
         return self._ensure_layer(layer_idx).update(key_states, value_states, kwargs)
+
+    def prefill_block_defers(self, layer_idx: int) -> bool:
+        """Whether a multi-token (prefill) block for this layer has to stay dense until the first decode step.
+
+        The reference defers every prefill block and quantizes all layers at the first decode forward
+        (muzero/integrations/transformers_patch.py:546-555), which keeps the dense K/V of every layer alive
+        through the prefill.  When ``generate()`` prefills in one forward (``single_shot_prefill``, set by the
+        generation hook), the layer's first block is the whole prompt: it is quantized inside its own ``update``
+        call, straight from the projection output.  The codes are the ones the deferred flush would produce (the
+        same tokens, the same whole-block alpha selection) and the prompt's own attention still sees the raw
+        block, so tokens do not change; what changes is that only the residual window stays dense.  A chunked
+        prefill keeps the reference's deferral: later chunks attend to the exact dense K/V of earlier ones."""
+        if not self.defer_prefill_quantization:
+            return False
+        first_block = layer_idx >= len(self.layers) or not self.layers[layer_idx].is_initialized
+        return not (self.single_shot_prefill and first_block)
 
     def finalize_prefill_quantization(self) -> None:
         for layer in self.layers:
@@ -254,6 +274,7 @@ def _wrap_cache_preparation() -> None:
         hint = max_cache_length if isinstance(max_cache_length, int) and max_cache_length > 0 else None
         cache = MuZeroCache(MuZeroConfig.from_dict(cache_config), max_cache_length=hint)
         cache.defer_prefill_quantization = True
+        cache.single_shot_prefill = getattr(generation_config, "prefill_chunk_size", None) is None
         model_kwargs["past_key_values"] = cache
         return None
 
@@ -316,8 +337,12 @@ def _wrap_attention_forward(module, cls_name: str, qk_norm: bool) -> None:
         k, v = cache.update(k, v, self.layer_idx, {
             "sin": sin, "cos": cos, "cache_position": kwargs.get("cache_position"),
             "materialize_full_kv": not fused,
-            "defer_quantize": bool(cache.defer_prefill_quantization and q.shape[-2] > 1),
+            "defer_quantize": bool(q.shape[-2] > 1 and cache.prefill_block_defers(self.layer_idx)),
         })
+        if fused and cache.parity_mode:
+            from ..cache.attention import decode_attention_reference_rounding
+            out = decode_attention_reference_rounding(cache.layers[self.layer_idx], q, self.scaling, attention_mask)
+            return self.o_proj(out.reshape(*batch_shape, -1).contiguous()), None
         if fused:
             kwargs["kv_cache_state"] = cache.get_attention_state(self.layer_idx)
             attend = module.eager_attention_forward

@@ -1,6 +1,7 @@
 """Golden greedy tokens of the reference itself: a random-init Qwen3-architecture decoder run on
 CPU through the reference's `patch_transformers()` + `generate(cache_implementation="mu_zero_4bit",
-backend="torch")`.  Writes generate_case.json (token ids + the model/prompt recipe).
+backend="torch")`.  Writes generate_case.json (token ids + the model/prompt recipe) and generate_logits.npz
+(the reference's fp32 logits of every generated position, [batch, new_tokens, vocab]).
 
     python tests/golden/make_generate_golden.py [--reference /path/to/reference]
 """
@@ -16,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 MODEL = dict(num_hidden_layers=2, hidden_size=256, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
              intermediate_size=512, vocab_size=1024, max_position_embeddings=2048, rms_norm_eps=1e-6,
              rope_theta=1e6, tie_word_embeddings=False)
-RECIPE = dict(model=MODEL, weight_seed=0, weight_std=0.02, prompt_seed=1, batch=2, prompt_len=300, new_tokens=48,
+RECIPE = dict(model=MODEL, weight_seed=0, weight_std=0.02, prompt_seed=1, batch=2, prompt_len=300, new_tokens=96,
               cache_implementation="mu_zero_4bit", cache_config={"q_group_size": 64, "residual_length": 128})
 
 
@@ -52,8 +53,12 @@ def main():
     cfg = dict(RECIPE["cache_config"], backend="torch")
     out = model.generate(input_ids=ids, attention_mask=torch.ones_like(ids), max_new_tokens=RECIPE["new_tokens"],
                          do_sample=False, cache_implementation=RECIPE["cache_implementation"], cache_config=cfg,
-                         pad_token_id=0)
+                         pad_token_id=0, output_logits=True, return_dict_in_generate=True)
     stats = muzero.get_mu_zero_decode_stats()
+    logits = torch.stack([x.float() for x in out.logits], dim=1)          # [batch, new_tokens, vocab]
+    out = out.sequences
+    import numpy as np
+    np.savez_compressed(os.path.join(HERE, "generate_logits.npz"), logits=logits.numpy())
     result = dict(recipe=RECIPE, tokens=out[:, ids.shape[1]:].tolist(), reference_decode_stats=stats,
                   torch=torch.__version__)
     with open(os.path.join(HERE, "generate_case.json"), "w") as f:
