@@ -103,7 +103,11 @@ def decode_attention(layer, query: torch.Tensor, scaling: float, attention_mask:
     """[B,H,1,D] query -> [B,1,H,D] attention output over ``layer``'s prefix + residual."""
     b, h, _, d = query.shape
     if layer._key_group_count * layer.q_group_size != layer._value_storage_len:
-        return _decode_attention_unaligned(layer, query, scaling, attention_mask, out_dtype or query.dtype)
+        # value prefix ahead of the key prefix (logq_compatible_layout): the tiled kernel reads the early values
+        # from the packed store; shapes it does not serve take the two-kernel route
+        kvh = layer.keys.shape[1]
+        if not (d == 128 and layer.q_group_size in (32, 64, 128) and h % kvh == 0 and h // kvh in (1, 2, 4, 8)):
+            return _decode_attention_unaligned(layer, query, scaling, attention_mask, out_dtype or query.dtype)
     out = torch.empty((b, 1, h, d), dtype=out_dtype or query.dtype, device=query.device)
     args = build_decode_args(layer, query, scaling, attention_mask, out, splits=splits)
     with torch.cuda.device(query.device):
@@ -116,10 +120,10 @@ def _decode_attention_unaligned(layer, query: torch.Tensor, scaling: float, atte
                                 out_dtype: torch.dtype) -> torch.Tensor:
     """Decode attention when the value prefix is ahead of the key prefix (``logq_compatible_layout``).
 
-    The fused kernel pairs key and value tiles of the same tokens, which this legacy layout does not
-    offer; this route is the reference's own structure (muzero/cache/attention.py:104-151,186-263) in
-    fp32: packed keys through ``mz_qk_logits``, packed values through ``mz_av_output``, the two dense
-    residual pieces and the softmax in torch.  It is the slow path of a compatibility flag."""
+    Only for shapes outside the tiled kernel (head_dim other than 128, ...): the reference's own structure
+    (muzero/cache/attention.py:104-151,186-263) in fp32: packed keys through ``mz_qk_logits``, packed values
+    through ``mz_av_output``, the two dense residual pieces and the softmax in torch.  Head_dim 128 caches go
+    through the fused kernel, which takes the early values from the packed store."""
     from ..kernels.loader import ensure_expand_table
     if not query.is_cuda:
         raise MuZeroKernelError("decode attention needs CUDA tensors; this package has no CPU path")

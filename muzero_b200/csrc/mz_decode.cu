@@ -76,10 +76,11 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   int rc = mz_check_store_basic(s);
   if (rc) return rc;
   MZ_REQUIRE(a->q_heads > 0 && a->q_heads % s->kv_heads == 0, "q_heads %d is not a multiple of kv_heads %d", a->q_heads, s->kv_heads);
-  MZ_REQUIRE(s->k_groups * s->group == s->v_tokens, "key prefix (%d tokens) and value prefix (%d tokens) differ", s->k_groups * s->group,
-             s->v_tokens);
+  const int v_lead = s->v_tokens - s->k_groups * s->group;
+  MZ_REQUIRE(v_lead >= 0 && v_lead <= s->res_len, "value prefix (%d tokens) must cover the key prefix (%d tokens) and end inside the residual window (%d tokens)",
+             s->v_tokens, s->k_groups * s->group, s->res_len);
   MZ_REQUIRE(s->k_groups > 0 || s->res_len > 0, "no tokens to attend to");
-  if (s->k_groups > 0 && (rc = mz_check_store_quantized(s))) return rc;
+  if ((s->k_groups > 0 || v_lead > 0) && (rc = mz_check_store_quantized(s))) return rc;
   if (s->res_len > 0 && (rc = mz_check_store_residual(s))) return rc;
   MZ_REQUIRE(a->query != nullptr, "query is NULL");
   MZ_REQUIRE(a->mask == nullptr || mz_dtype_ok(a->mask_dtype), "bad mask dtype");
@@ -94,9 +95,12 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   p.QB = mz_row_bytes(s->group, s->bits);
   p.NG = (s->head_dim + s->group - 1) / s->group;
   p.eps = 1e-8f;
+  p.v_lead = v_lead;
   p.table_k = p.table_v = nullptr;
   const int force = kernel_override();
   plan->tiles = force != 1 && mz_decode_tiles_supported(p);
+  if (v_lead > 0 && !plan->tiles)
+    return mz_fail(MZ_ERR_UNSUPPORTED, "a value prefix ahead of the key prefix is served by the tiled kernel only (head_dim 128, group 32/64/128)");
   if (plan->tiles) {
     if (force == 0 && mz_decode_mma_supported(p)) rc = mz_plan_mma(p, a->splits, sm_count(), &plan->slots);
     else rc = mz_plan_tiles(p, a->splits, sm_count(), &plan->slots);

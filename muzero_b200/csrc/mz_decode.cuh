@@ -65,6 +65,9 @@ struct MzDecodeParams {
   const float* table_k;  // exact expand tables (generic kernel)
   const float* table_v;
   float eps;
+  // value prefix tokens beyond the key prefix (logq_compatible_layout): the first v_lead tokens of the residual
+  // window have their values in the packed store (rows k_groups*G ..), the rest in the dense window
+  int v_lead;
   MzTilesPlan tp;
 };
 

@@ -750,7 +750,7 @@ static int window_base() {
 bool mz_decode_mma_supported(const MzDecodeParams& p) {
   const mz_kv_store& s = p.s;
   if (!mz_decode_tiles_supported(p)) return false;
-  if (s.group != 64 || (s.bits != 2 && s.bits != 4)) return false;
+  if (s.group != 64 || (s.bits != 2 && s.bits != 4) || p.v_lead != 0) return false;
   if (p.gqa != 1 && p.gqa != 2 && p.gqa != 4) return false;
   // the residual-tile path reads the query in 4-byte pieces
   if (((uintptr_t)p.query & 3) || ((p.q_stride_b | p.q_stride_h) & 1)) return false;

@@ -119,6 +119,30 @@ __device__ __forceinline__ void softmax_tile(const Warp<BITS, G, GQA>& w, float 
   }
 }
 
+// Two neighbouring codes (idx, idx + 1) of a packed row in global memory, dequantized with the reference's fp32
+// formula (muzero/quantizer.py:229-255; expm1 evaluated directly).  Cold path: residual tokens whose values
+// were flushed ahead of their keys.
+template <int BITS>
+__device__ __noinline__ float2 dequant_pair(const uint8_t* row, int idx, int row_bytes, float lo, float span, float alpha) {
+  const MzRowParams r = mz_row_params(lo, span, (1 << BITS) - 1, 1e-8f);
+  const float lb = log1pf(alpha);
+  float out[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int q = mz_extract_code(row, idx + i, BITS, row_bytes);
+    float unit;
+    if (q >= r.zero_code) {
+      const float grow = expm1f((float)min(q - r.zero_code, r.steps_up) / (float)r.steps_up * lb) / alpha;
+      unit = r.anchor + r.room_up * grow;
+    } else {
+      const float grow = expm1f((float)min(r.zero_code - q, r.steps_dn) / (float)r.steps_dn * lb) / alpha;
+      unit = r.anchor - r.room_dn * grow;
+    }
+    out[i] = fminf(fmaxf(unit, 0.0f), 1.0f) * span + lo;
+  }
+  return make_float2(out[0], out[1]);
+}
+
 template <int BITS, int G, int GQA>
 __global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_tiles_kernel(const MzDecodeParams p) {
   using C = Cfg<BITS, G, GQA>;
@@ -501,11 +525,23 @@ __global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_t
         float ph[GQA];
 #pragma unroll
         for (int h = 0; h < GQA; ++h) ph[h] = w.pbuf[t * GQA + h];
+        // a residual token whose value already sits in the packed store (the value prefix runs ahead of the
+        // key prefix): its channels are dequantized from there in fp32, the stale window row is not used
+        const bool from_store = tok0 + t < p.v_lead;
+        const long long vrow = (long long)nq + tok0 + t;
 #pragma unroll
         for (int g = 0; g < C::NG; ++g)
 #pragma unroll
           for (int k = 0; k < C::TPL; k += 2) {
-            const float2 x = unpack2(*(const uint32_t*)(row + g * G + k), s.kv_dtype);
+            float2 x;
+            if (from_store) {
+              const uint8_t* pr = s.packed_v + b * s.pv_stride_b + kvh * s.pv_stride_h + (vrow * C::NG + g) * C::QB;
+              const long long mi = b * s.vm_stride_b + kvh * s.vm_stride_h + vrow * C::NG + g;
+              x = dequant_pair<BITS>(pr, w.q16 * C::TPL + k, C::QB, mz_load_as_float(s.v_mn, mi, s.meta_dtype),
+                                     mz_load_as_float(s.v_scale, mi, s.meta_dtype), s.alpha_value);
+            } else {
+              x = unpack2(*(const uint32_t*)(row + g * G + k), s.kv_dtype);
+            }
 #pragma unroll
             for (int h = 0; h < GQA; ++h) ffma2(out2[g * (C::TPL / 2) + k / 2][h], x, make_float2(ph[h], ph[h]));
           }

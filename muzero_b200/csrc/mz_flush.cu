@@ -48,17 +48,32 @@ __device__ void flush_key_tile(const FlushParams& p, uint16_t* tile) {
   const int grp = s.k_groups + j;
   uint8_t* dst_rows = s.packed_k + b * s.pk_stride_b + h * s.pk_stride_h + (long long)grp * D * p.QB;
   const long long meta0 = b * s.km_stride_b + h * s.km_stride_h + (long long)grp * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  // A channel's G tokens are split over `parts` threads when the CTA has more threads than channels (2 for
+  // head_dim 128 and 256 threads): partial min/max meet in shared memory, then each thread quantizes and packs
+  // its own share of the row (whole octets, so the byte ranges of the parts do not overlap).
+  const int parts = (blockDim.x >= 2 * D && G % 16 == 0) ? 2 : 1;
+  float* red = (float*)(tile + ((G * D + 1) & ~1));          // [parts][2][D]
+  const int share = G / parts;
+  for (int idx = threadIdx.x; idx < D * parts; idx += blockDim.x) {
+    const int d = idx % D, part = idx / D;
     float mn = INFINITY, mx = -INFINITY;
-    for (int t = 0; t < G; ++t) {
+    for (int t = part * share; t < (part + 1) * share; ++t) {
       const float v = mz_u16_to_float(tile[t * D + d], DT);
       mn = fminf(mn, v); mx = fmaxf(mx, v);
     }
+    red[(part * 2) * D + d] = mn;
+    red[(part * 2 + 1) * D + d] = mx;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < D * parts; idx += blockDim.x) {
+    const int d = idx % D, part = idx / D;
+    float mn = red[d], mx = red[D + d];
+    if (parts == 2) { mn = fminf(mn, red[2 * D + d]); mx = fmaxf(mx, red[3 * D + d]); }
     MzQuantRow<DT> r;
     r.setup(mn, mx, s.bits, s.alpha_key, p.eps, p.ctab_k, p.ctab_k_n);
     uint8_t* dst = dst_rows + (long long)d * p.QB;
-    for (int t0 = 0; t0 < G; t0 += 8) {
-      const int n = min(8, G - t0);
+    for (int t0 = part * share; t0 < (part + 1) * share; t0 += 8) {
+      const int n = min(8, (part + 1) * share - t0);
       unsigned long long word = 0;
       for (int k = 0; k < n; ++k)
         word |= ((unsigned long long)r.code(mz_u16_to_float(tile[(t0 + k) * D + d], DT))) << (k * s.bits);
@@ -69,8 +84,10 @@ __device__ void flush_key_tile(const FlushParams& p, uint16_t* tile) {
         for (int i = 0; i < nb; ++i) o[i] = (uint8_t)(word >> (8 * i));
       }
     }
-    mz_store_from_float(s.k_mn, meta0 + d, r.lo, s.meta_dtype);
-    mz_store_from_float(s.k_scale, meta0 + d, r.span, s.meta_dtype);
+    if (part == 0) {
+      mz_store_from_float(s.k_mn, meta0 + d, r.lo, s.meta_dtype);
+      mz_store_from_float(s.k_scale, meta0 + d, r.span, s.meta_dtype);
+    }
   }
 }
 
@@ -279,7 +296,7 @@ extern "C" int mz_flush_kv_parts(const mz_kv_store* s, int n_key_tokens, int val
   const long long vb = (p.v_rows + rows_per_cta - 1) / rows_per_cta;
   MZ_REQUIRE(kb + vb < (1LL << 31), "flush too large");
   p.n_k_blocks = (unsigned)kb;
-  const size_t smem = (size_t)g.G * g.D * 2;
+  const size_t smem = (size_t)((g.G * g.D + 1) & ~1) * 2 + (size_t)g.D * 4 * sizeof(float);   // key tile + partial min/max of two parts
   if (smem > 200 * 1024) return mz_fail(MZ_ERR_UNSUPPORTED, "key tile of %zu bytes exceeds shared memory", smem);
   cudaStream_t st = (cudaStream_t)stream;
   if (g.kv_dt == MZ_BF16) {

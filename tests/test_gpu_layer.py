@@ -249,10 +249,16 @@ def test_decode_step_with_mask_and_refusals(oracle):
 
 @pytest.mark.parametrize("hf_strides", [False, True])
 @pytest.mark.parametrize("name", ["c4g64_logq", "c4g64_logq_dec", "c2g32_logq_dec"])
-def test_logq_layout_matches_reference(oracle, golden, name, hf_strides):
+def test_logq_layout_matches_reference(oracle, golden, name, hf_strides, monkeypatch):
     """`logq_compatible_layout=True`: keys flush by whole groups, values token by token, so the value
-    prefix runs ahead; store, residual windows and attention against the reference's own run."""
+    prefix runs ahead; store, residual windows and attention against the reference's own run.  The
+    attention goes through the fused kernel (the two-kernel route is for other head sizes only)."""
+    from muzero_b200.cache import attention as attention_module
     from muzero_b200.cache.attention import decode_attention
+
+    def not_here(*a, **kw):
+        raise AssertionError("head_dim 128 must take the fused kernel")
+    monkeypatch.setattr(attention_module, "_decode_attention_unaligned", not_here)
     meta, g = golden.layer_logq_meta[name], golden.layer_logq
     layer, q = gpu_layer_from_meta(oracle, meta, hf_strides)
     assert np.array_equal(layer._packed_key_q.cpu().numpy(), g[name + "/packed_k"])
