@@ -142,6 +142,19 @@ int mz_append_kv(const mz_kv_store* store, const void* k_new, const void* v_new,
 int mz_dequantize_kv(const mz_kv_store* store, int g0, int g1, void* out_k,
                      int t0, int t1, void* out_v, int out_dtype, float eps, void* stream);
 
+/*
+ * Re-indexes a whole layer cache along the batch in one launch: entry i of dst takes entry index[i] of
+ * src (index: int64 on the device), for the valid part of all eight tensors (packed codes and metadata
+ * of keys and values, residual window).  dst has the same shape parameters, its own buffers with the
+ * capacities it needs, and res_start where the window shall land; the caller sets dst's counters
+ * (k_groups, v_tokens, res_len as in src).  *status (a device int the caller zeroed) becomes 1 if an
+ * index lies outside [0, src->batch); that entry is skipped.
+ * Replaces: the per-tensor indexing of reorder_cache / batch_select_indices / batch_repeat_interleave,
+ * muzero/cache/layer.py:508-523.
+ */
+int mz_store_gather_batch(const mz_kv_store* src, const mz_kv_store* dst, const long long* index, int* status,
+                          void* stream);
+
 /* One decode-attention call. */
 typedef struct mz_decode_args {
   mz_kv_store store;

@@ -495,12 +495,20 @@ class MuZeroCacheLayer:
         return k, v
 
     def crop(self, max_length: int) -> None:
+        """Keeps the first ``max_length`` tokens.  As in the reference (muzero/cache/layer.py:494-506) the kept
+        tokens become a dense window again and are re-quantized by the next update; only the groups / tokens
+        that survive are dequantized (the reference materialises the whole cache and slices it)."""
         if max_length < 0:
             max_length = max(0, self.get_seq_length() + max_length)
         if max_length >= self.get_seq_length():
             return
-        k, v = self._full_kv()
-        k, v = k[..., :max_length, :].contiguous(), v[..., :max_length, :].contiguous()
+        g = self.q_group_size
+        nk, nv = self._key_group_count * g, self._value_storage_len
+        k_pre = self._dequantize(0, min(self._key_group_count, -(-max_length // g)), 0, 0, True, False)[0] if nk else None
+        v_pre = self._dequantize(0, 0, 0, min(nv, max_length), False, True)[1] if nv else None
+        k = torch.cat([k_pre, self.keys], dim=2)[..., :max_length, :] if k_pre is not None else self.keys[..., :max_length, :]
+        v = torch.cat([v_pre, self.values], dim=2)[..., :max_length, :] if v_pre is not None else self.values[..., :max_length, :]
+        k, v = k.contiguous(), v.contiguous()
         self.reset()
         if max_length > 0:
             self.lazy_initialization(k[:, :, :1], v[:, :, :1])
@@ -508,6 +516,7 @@ class MuZeroCacheLayer:
             self.cumulative_length = max_length
 
     def _reindex_batch(self, fn) -> None:
+        """Generic batch re-indexing with tensor ops (state that is not on a GPU)."""
         if self.keys is not None and self.keys.dim() == 4:
             # also with zero residual tokens (residual_length=0 right after a flush): the window's shape
             # carries the batch size, and its old buffers belong to the old batch
@@ -520,25 +529,97 @@ class MuZeroCacheLayer:
             self._adopt_store({"pk": fn(b["pk"][:, :, :kg]), "kmn": fn(b["kmn"][:, :, :kg]), "ksc": fn(b["ksc"][:, :, :kg]),
                                "pv": fn(b["pv"][:, :, :vt]), "vmn": fn(b["vmn"][:, :, :vt]), "vsc": fn(b["vsc"][:, :, :vt])})
 
+    def _gather_batch(self, index: torch.Tensor) -> None:
+        """Entry i of the new cache := entry ``index[i]`` of the current one, all eight tensors in one launch
+        (``mz_store_gather_batch``); the reference indexes tensor by tensor (muzero/cache/layer.py:508-523)."""
+        if not self.is_initialized or self.keys is None or self.keys.dim() != 4:
+            return
+        if not self.keys.is_cuda or self._value_lead:
+            self._reindex_batch(lambda t: t[index.to(t.device), ...])
+            return
+        index = index.to(device=self.device, dtype=torch.int64).contiguous()
+        n, kvh = int(index.numel()), self.keys.shape[1]
+        cur = int(self.keys.shape[2])
+        if self._key_buffer is None:
+            self._rehome_residual(cur + 1)
+        src = self._store_struct()
+        # the source stays alive during the launch, and comes back if an index turns out to be out of range
+        old = (self._bufs, self._key_buffer, self._value_buffer, self._res_start, self._keys, self._values)
+        cap = self._buffer_capacity
+        kb = torch.empty((n, kvh, cap, self.k_head_dim), dtype=self.dtype, device=self.device)
+        vb = torch.empty((n, kvh, cap, self.v_head_dim), dtype=self.dtype, device=self.device)
+        new = {name: torch.empty((n, *t.shape[1:]), dtype=t.dtype, device=self.device) for name, t in self._bufs.items()}
+        self._bufs, self._key_buffer, self._value_buffer, self._res_start = new, kb, vb, 0
+        self._step_args = None
+        self._keys, self._values = kb[:, :, :cur], vb[:, :, :cur]
+        self._window_stale = False
+        dst = self._store_struct()
+        status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            check(load_mu_zero_cuda_extension().mz_store_gather_batch(
+                ctypes.byref(src), ctypes.byref(dst), index.data_ptr(), status.data_ptr(), stream_ptr(self.device)),
+                "mz_store_gather_batch")
+        if int(status.item()):
+            self._bufs, self._key_buffer, self._value_buffer, self._res_start, self._keys, self._values = old
+            self._step_args = None
+            self._refresh_views()
+            raise MuZeroKernelError("batch index out of range")
+        del old
+        self._refresh_views()
+
     def batch_repeat_interleave(self, repeats: int) -> None:
-        self._reindex_batch(lambda t: t.repeat_interleave(repeats, dim=0))
+        if self.is_initialized and self.keys is not None and self.keys.dim() == 4:
+            self._gather_batch(torch.arange(self.keys.shape[0]).repeat_interleave(repeats))
 
     def batch_select_indices(self, indices: torch.Tensor) -> None:
-        self._reindex_batch(lambda t: t[indices, ...])
+        self._gather_batch(indices)
 
     def reorder_cache(self, beam_idx: torch.LongTensor) -> None:
-        self.batch_select_indices(beam_idx.to(self.device))
+        self._gather_batch(beam_idx)
 
+    # offload / prefetch: the valid part of every tensor moves to pinned host memory and back on a side
+    # stream, so that the copies neither block the host nor serialise with the compute stream's kernels
     def offload(self) -> None:
-        if self.is_initialized:
-            self._reindex_batch(lambda t: t.to("cpu", non_blocking=True))
+        if not self.is_initialized or self.keys is None or not self.keys.is_cuda:
+            return
+        side = _side_stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+
+        def to_host(t: torch.Tensor) -> torch.Tensor:
+            host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            host.copy_(t, non_blocking=True)
+            t.record_stream(side)
+            return host
+        with torch.cuda.stream(side):
+            self._reindex_batch(to_host)
+        self._offload_done = torch.cuda.Event()
+        self._offload_done.record(side)
 
     def prefetch(self) -> None:
-        if self.is_initialized and self.keys is not None and self.keys.device != self.device:
+        if not self.is_initialized or self.keys is None or self.keys.device == self.device:
+            return
+        side = _side_stream(self.device)
+        done = getattr(self, "_offload_done", None)
+        if done is not None:
+            side.wait_event(done)
+        with torch.cuda.stream(side):
             self._reindex_batch(lambda t: t.to(self.device, non_blocking=True))
+        torch.cuda.current_stream(self.device).wait_stream(side)
 
     def reset(self) -> None:
         self._clear_state()
+
+
+_side_streams: dict = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    """One copy stream per device for cache offload / prefetch."""
+    st = _side_streams.get(device)
+    if st is None:
+        st = torch.cuda.Stream(device)
+        _side_streams[device] = st
+    return st
 
 
 def _select_alpha_value_block(block: torch.Tensor, *, bits: int, group: int, d_pad: int, max_points: int) -> float:

@@ -139,10 +139,22 @@ def test_crop_reorder_offload(oracle):
     layer.batch_select_indices(torch.tensor([2, 0], device="cuda"))
     sel_k, _ = layer._full_kv()
     assert torch.equal(sel_k, full_k[[2, 0]])
-    layer.offload(); layer.prefetch()
+    layer.offload()
+    assert not layer.keys.is_cuda and layer._packed_key_q.is_pinned()
+    layer.prefetch()
     assert torch.equal(layer._full_kv()[0], full_k[[2, 0]])
+    # beam-search style reorder with a repeated entry, then a repeat-interleave; decoding goes on afterwards
+    layer.reorder_cache(torch.tensor([1, 1, 0], device="cuda"))
+    assert torch.equal(layer._full_kv()[0], full_k[[0, 0, 2]])
+    layer.batch_repeat_interleave(2)
+    want = full_k[[0, 0, 0, 0, 2, 2]]
+    assert torch.equal(layer._full_kv()[0], want) and layer.keys.shape[0] == 6
+    layer.update(k[[0, 0, 0, 0, 2, 2], :, :1].cuda(), v[[0, 0, 0, 0, 2, 2], :, :1].cuda(), {"materialize_full_kv": False})
+    assert layer.get_seq_length() == 401 and torch.equal(layer._full_kv()[0][:, :, :400], want)
+    with pytest.raises(Exception):
+        layer.batch_select_indices(torch.tensor([7], device="cuda"))
     layer.crop(100)
-    assert layer.get_seq_length() == 100 and torch.equal(layer.keys, full_k[[2, 0], :, :100])
+    assert layer.get_seq_length() == 100 and torch.equal(layer.keys, want[:, :, :100])
 
 
 def test_batch_select_with_empty_residual_window(oracle):
