@@ -171,6 +171,16 @@ typedef struct mz_decode_args {
   void* workspace; size_t workspace_bytes;
 } mz_decode_args;
 
+/*
+ * Testing aid: selects the decode-attention kernel for later calls of this process and returns the previous
+ * selection.  0 = automatic, 1 = shape-generic kernel, 2 = SIMT tiled kernel (no tensor cores), 3 = automatic,
+ * 4 = tcgen05 / tensor-memory kernel where it applies (head_dim 128, group 64, 2- or 4-bit codes).  The
+ * environment variable MZ_DECODE_KERNEL = generic | tiles | mma | umma gives the initial selection.  Workspace
+ * sizes depend on the selection: query them again after changing it.  No counterpart in the reference, which
+ * picks its kernels by shape only (muzero/kernels/loader.py:1382-1440).
+ */
+int mz_debug_force_kernel(int which);
+
 /* Bytes of workspace mz_decode_attention needs for these arguments (splits resolved as the call would). */
 size_t mz_decode_workspace_bytes(const mz_decode_args* args);
 

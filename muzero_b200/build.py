@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libmuzero_b200.so")
-SOURCES = ["mz_tables.cu", "mz_rows.cu", "mz_flush.cu", "mz_decode.cu", "mz_decode_generic.cu", "mz_decode_tiles.cu", "mz_decode_mma.cu", "mz_qkav.cu", "mz_decode_static.cu", "mz_step.cu", "mz_manage.cu"]
+SOURCES = ["mz_tables.cu", "mz_rows.cu", "mz_flush.cu", "mz_decode.cu", "mz_decode_generic.cu", "mz_decode_tiles.cu", "mz_decode_mma.cu", "mz_decode_umma.cu", "mz_qkav.cu", "mz_decode_static.cu", "mz_step.cu", "mz_manage.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--fmad=true", "-Xptxas", "-v",

@@ -2,6 +2,7 @@
 // kernel dispatch, and the deterministic log-sum-exp combine.
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "mz_decode.cuh"
@@ -55,16 +56,25 @@ int sm_count() {
   return g_sm_count[dev];
 }
 
-// MZ_DECODE_KERNEL (read once, at the first call): "generic" routes every call to the shape-generic
-// kernel and "tiles" keeps the tensor-core kernel off, so that tests can cross-check the three kernels
-// against each other on the same device.  0 = automatic, 1 = generic, 2 = tiles.
+// Which decode kernel serves a call.  0 = automatic (tensor-core mma.sync kernel where it applies, else the SIMT
+// tiled kernel, else the shape-generic kernel), 1 = generic, 2 = no tensor-core kernel, 3 = the same as 0,
+// 4 = the tcgen05 kernel where it applies (an opt-in: correct, but slower than the mma.sync kernel so far).
+// MZ_DECODE_KERNEL = generic | tiles | mma | umma sets the initial value (read once, at the first call);
+// mz_debug_force_kernel changes it for later calls, so that tests can cross-check the kernels in one process.
+std::atomic<int> g_kernel_override{-1};
 int kernel_override() {
-  static const int v = [] {
+  int v = g_kernel_override.load(std::memory_order_relaxed);
+  if (v < 0) {
     const char* e = std::getenv("MZ_DECODE_KERNEL");
-    if (e && std::strcmp(e, "generic") == 0) return 1;
-    if (e && std::strcmp(e, "tiles") == 0) return 2;
-    return 0;
-  }();
+    v = 0;
+    if (e && std::strcmp(e, "generic") == 0) v = 1;
+    if (e && std::strcmp(e, "tiles") == 0) v = 2;
+    if (e && std::strcmp(e, "mma") == 0) v = 3;
+    if (e && std::strcmp(e, "umma") == 0) v = 4;
+    int expected = -1;
+    g_kernel_override.compare_exchange_strong(expected, v);
+    v = g_kernel_override.load(std::memory_order_relaxed);
+  }
   return v;
 }
 
@@ -102,7 +112,10 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   if (v_lead > 0 && !plan->tiles)
     return mz_fail(MZ_ERR_UNSUPPORTED, "a value prefix ahead of the key prefix is served by the tiled kernel only (head_dim 128, group 32/64/128)");
   if (plan->tiles) {
-    if (force == 0 && mz_decode_mma_supported(p)) rc = mz_plan_mma(p, a->splits, sm_count(), &plan->slots);
+    p.tp2 = MzTilesPlan{};
+    p.slots_a = 0;
+    if (force == 4 && mz_decode_umma_supported(p)) rc = mz_plan_umma(p, a->splits, sm_count(), &plan->slots);
+    else if (force != 2 && mz_decode_mma_supported(p)) rc = mz_plan_mma(p, a->splits, sm_count(), &plan->slots);
     else rc = mz_plan_tiles(p, a->splits, sm_count(), &plan->slots);
     if (rc) return rc;
     p.splits = 0;
@@ -120,6 +133,9 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
     p.splits = splits;
     plan->slots = (size_t)s->batch * a->q_heads * splits;
   }
+  // the three arrays (m, l, acc) follow each other in the workspace; a record count that is a multiple of 4 keeps
+  // the acc rows 16-byte aligned (the kernels store them as vectors)
+  plan->slots = (plan->slots + 3) & ~(size_t)3;
   plan->ws_bytes = plan->slots * sizeof(float) * (2 + (size_t)s->head_dim);
   if (need_tables && !plan->tiles) {
     if ((rc = mz_get_expand_table(s->bits, s->alpha_key, &p.table_k))) return rc;
@@ -138,6 +154,7 @@ int launch_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
   p.part.l = p.part.m + plan->slots;
   p.part.acc = p.part.l + plan->slots;
   if (!plan->tiles) return mz_launch_decode_generic(p, st);
+  if (p.tp.kind == 2) return mz_launch_decode_umma(p, st);
   return p.tp.kind == 1 ? mz_launch_decode_mma(p, st) : mz_launch_decode_tiles(p, st);
 }
 
@@ -182,6 +199,12 @@ int mz_decode_run_plan(const mz_decode_args* a, MzDecodePlan* plan, cudaStream_t
   return finish(*plan, o, st);
 }
 
+extern "C" int mz_debug_force_kernel(int which) {
+  const int before = kernel_override();
+  if (which >= 0 && which <= 4) g_kernel_override.store(which, std::memory_order_relaxed);
+  return before;
+}
+
 extern "C" size_t mz_decode_workspace_bound(const mz_decode_args* a) {
   if (a == nullptr || mz_check_store_basic(&a->store) != MZ_OK) return 0;
   const mz_kv_store& s = a->store;
@@ -191,13 +214,14 @@ extern "C" size_t mz_decode_workspace_bound(const mz_decode_args* a) {
   }
   const long long pairs = (long long)s.batch * s.kv_heads, gqa = a->q_heads / s.kv_heads;
   const long long sms = sm_count();
-  // tiled kernels: slots = W * max_segs * gqa <= gqa * (pairs + 3 W), W <= 12 warps per SM (or pairs * splits)
-  const long long w_max = a->splits > 0 ? pairs * a->splits : sms * 12;
-  const long long tiled = gqa * (pairs + 3 * w_max);
+  // tiled kernels: slots = W * max_segs * gqa <= gqa * (pairs + 3 W) per plan; at most two plans (packed and
+  // residual tiles) with W <= 3 + 12 workers per SM (or pairs * splits + pairs)
+  const long long w_max = a->splits > 0 ? pairs * (a->splits + 1) : sms * 15;
+  const long long tiled = gqa * (2 * pairs + 3 * w_max);
   // generic kernel: one slot per (batch, head, split)
   const long long splits = a->splits > 0 ? a->splits : (2 * sms * 4 + pairs - 1) / pairs;
   const long long generic = (long long)s.batch * a->q_heads * (splits < 1 ? 1 : splits);
-  return (size_t)(tiled > generic ? tiled : generic) * sizeof(float) * (2 + (size_t)s.head_dim);
+  return (size_t)((tiled > generic ? tiled : generic) + 3) * sizeof(float) * (2 + (size_t)s.head_dim);
 }
 
 extern "C" size_t mz_decode_workspace_bytes(const mz_decode_args* args) {

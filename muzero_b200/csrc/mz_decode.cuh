@@ -69,6 +69,10 @@ struct MzDecodeParams {
   // window have their values in the packed store (rows k_groups*G ..), the rest in the dense window
   int v_lead;
   MzTilesPlan tp;
+  // tcgen05 route: the packed tiles run on plan `tp`, the residual tiles on plan `tp2` (mma.sync kernel,
+  // total_warps == 0 when there is no residual window); the records of tp2 start at record slots_a
+  MzTilesPlan tp2;
+  long long slots_a;
 };
 
 // where a call's result goes: normalised output, or the merged (m, l, acc) triple.  The triple is addressed
@@ -106,3 +110,10 @@ int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t
 bool mz_decode_mma_supported(const MzDecodeParams& p);
 int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots);
 int mz_launch_decode_mma(const MzDecodeParams& p, cudaStream_t st);
+int mz_smem_window_base();
+
+// tcgen05 kernel (A operand in tensor memory): the packed tiles of head_dim 128 / group 64 / 2- or 4-bit caches;
+// the residual tiles go to the mma.sync kernel in a companion launch
+bool mz_decode_umma_supported(const MzDecodeParams& p);
+int mz_plan_umma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots);
+int mz_launch_decode_umma(const MzDecodeParams& p, cudaStream_t st);

@@ -30,21 +30,12 @@
 // combine_tiles_kernel.
 #include <mutex>
 
-#include "mz_tiles_common.cuh"
+#include "mz_mma_common.cuh"
 
 namespace mzm {
-using mzt::cp_async_commit;
-using mzt::cp_async_wait;
-using mzt::D;
-using mzt::ex2f;
-using mzt::LOG2E;
-using mzt::prmt;
-
-constexpr int G = 64;                       // tokens per packed tile
 constexpr int DT = 16;                      // tokens per residual tile
 constexpr int DENSE_STRIDE = 2 * D + 16;    // padded row of a staged residual tile (bank spread)
 constexpr int DENSE_BYTES = DT * DENSE_STRIDE;
-constexpr uint32_t TBL = 65536;             // shared-window address of the lookup table
 constexpr int Z_BYTES = 128;                // zero codes of one tile side: [t][32 rows of lane class t], one byte each
 constexpr int RI_BYTES = Z_BYTES + 512;     // + fold constants: 64 x {half2(Bup, Bdn) of slot 0, of slot 1}
 constexpr int A_BYTES = 512;                // per-row constant A (fp32) of one tile side
@@ -52,64 +43,6 @@ constexpr int PBUF_BYTES = 1024;            // folded-probability source: [8 k-b
 constexpr int DBUF_BYTES = 256;             // residual-tile probabilities [16 tokens][4 heads] fp32; shares the value side's A array
 constexpr int MAX_WARPS = 12;
 
-// ---- shared memory by shared-window address (no generic-address arithmetic in the loops) ----
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t a) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float ldsf(uint32_t a) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
-__device__ __forceinline__ void sts16(uint32_t a, uint32_t v) {
-  asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory");
-}
-__device__ __forceinline__ void sts8(uint32_t a, uint32_t v) {
-  asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory");
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-  uint2 v;
-  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void stsf(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
-__device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
-  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void cp16(uint32_t sa, const void* g) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(g) : "memory");
-}
-__device__ __forceinline__ void warp_sync() { __syncwarp(); }
-
-// D(16x8, fp32) += A(16x16) * B(16x8), 16-bit operands of the named type
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
-__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
-__device__ __forceinline__ __half2 dup_lo(uint32_t v) { return __half2half2(__low2half(bits_h2(v))); }
-__device__ __forceinline__ __half2 dup_hi(uint32_t v) { return __half2half2(__high2half(bits_h2(v))); }
 
 // ---- lookup machinery.  A thread (g = lane / 4, t = lane % 4) holds the codes of two rows (the two
 // halves of the reduction block: slot 0 and slot 1) for eight consecutive positions 8g .. 8g+7 along
@@ -202,33 +135,10 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
   const int g = lane >> 2, t = lane & 3;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  // ---- the lookup table: entry (zc, e) -> half2(u+, u-), one copy per lane for keys and for values
-  for (int i = threadIdx.x; i < 2 * NE * NE; i += blockDim.x) {
-    const int which = i / (NE * NE), idx = i % (NE * NE);
-    const int zc = idx >> BITS, e = idx & TOP;
-    const float alpha = which ? s.alpha_value : s.alpha_key;
-    const float lb = log1pf(alpha);
-    // nominal ratio Bdn / Bup of a row in this zero-code bin (anchor at the bin centre); the end bins have
-    // codes on one side only and prep_rows makes their two constants equal
-    const float zac = (float)zc / (float)TOP;
-    const float ratio = (zc == 0 || zc == TOP) ? 1.0f : zac / (1.0f - zac);
-    __half2 ent;
-    if (e >= zc) {
-      const int up = max(TOP - zc, 1);
-      const float u = expm1f((float)min(e - zc, up) / (float)up * lb) / alpha;
-      const float uh = __half2float(__float2half_rn(u));
-      ent = __floats2half2_rn(uh, (u - uh) / ratio);
-    } else {
-      const int dn = max(zc, 1);
-      const float u = -expm1f((float)(zc - e) / (float)dn * lb) / alpha;
-      const float uh = __half2float(__float2half_rn(u));
-      ent = __floats2half2_rn((u - uh) * ratio, uh);
-    }
-    const uint32_t bits = h2_bits(ent);
-    const uint32_t row = TBL + idx * 256 + which * 128;
-#pragma unroll 4
-    for (int c = 0; c < 32; ++c) sts32(row + (((c + threadIdx.x) & 31) << 2), bits);
-  }
+  // tiles 0 .. kt-1 of a pair are packed groups, the rest residual tiles; a plan without packed tiles (the
+  // residual-only companion launch of the tcgen05 kernel) needs no table
+  const int kt = p.tp.packed_tiles;
+  if (kt > 0) fill_lookup_table<BITS>(s.alpha_key, s.alpha_value);
 
   const int W = p.tp.total_warps, T = p.tp.tiles_per_pair;
   const int gw = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -269,7 +179,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
   // residual tile: up to DT rows of 128 elements in padded rows; rows past the end are zeroed (they are
   // multiplied by probability 0, which must not meet a NaN bit pattern)
   auto stage_dense = [&](uint32_t dst, const uint16_t* res, int b, int kvh, int tile) {
-    const int tok0 = (tile - s.k_groups) * DT;
+    const int tok0 = (tile - kt) * DT;
     const int ntok = min(DT, s.res_len - tok0);
     const uint16_t* src = res + b * s.res_stride_b + kvh * s.res_stride_h + (long long)(s.res_start + tok0) * s.res_stride_t;
     for (int i = lane; i < DT * 16; i += 32) {
@@ -280,7 +190,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
   };
   auto stage_k = [&](const Cursor& c, bool valid) {
     if (valid) {
-      if (c.tile < s.k_groups) {
+      if (c.tile < kt) {
         const uint8_t* src = s.packed_k + c.b * s.pk_stride_b + c.kvh * s.pk_stride_h + (long long)c.tile * CODE_BYTES;
         for (int off = lane * 16; off < CODE_BYTES; off += 512) cp16(L.kbuf + off, src + off);
         const long long m0 = (c.b * s.km_stride_b + c.kvh * s.km_stride_h + (long long)c.tile * D) * msz;
@@ -296,7 +206,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
   };
   auto stage_v = [&](const Cursor& c, bool valid) {
     if (valid) {
-      if (c.tile < s.k_groups) {
+      if (c.tile < kt) {
         const uint8_t* src = s.packed_v + c.b * s.pv_stride_b + c.kvh * s.pv_stride_h + (long long)c.tile * CODE_BYTES;
         for (int i = lane; i < CODE_BYTES / 16; i += 32) {
           // 4-bit: a token's row is 64 bytes; its two 32-byte halves are swapped for tokens with bit 1 set so
@@ -335,18 +245,9 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
         lo = mz_u16_to_float((uint16_t)lds16(buf + CODE_BYTES + r * 2), s.meta_dtype);
         span = mz_u16_to_float((uint16_t)lds16(buf + CODE_BYTES + D * 2 + r * 2), s.meta_dtype);
       }
-      // IEEE division and multiply: the zero code must round exactly as the dequantizer's does
-      float anchor = __fdiv_rn(__fsub_rn(0.0f, lo), fmaxf(span, 1e-8f));
-      anchor = fminf(fmaxf(anchor, 0.0f), 1.0f);
-      const int zc = __float2int_rn(__fmul_rn(anchor, (float)TOP));
-      float A = fmaf(span, anchor, lo);
-      if (fabsf(A) <= 9.5367431640625e-7f * fmaxf(fabsf(lo), span)) A = 0.0f;
-      float Bup = fminf(span * fmaxf(1.0f - anchor, 1e-8f), 65504.f);
-      float Bdn = fminf(span * fmaxf(anchor, 1e-8f), 65504.f);
-      // a row whose zero code is the first / last code has no codes on the other side: that side's constant
-      // only ever multiplies the remainder half of the table entries (see the table)
-      if (zc == 0) Bdn = Bup;
-      if (zc == TOP) Bup = Bdn;
+      int zc;
+      float A, Bup, Bdn;
+      row_constants<BITS>(lo, span, zc, A, Bup, Bdn);
       any |= A != 0.0f;
       const int pos = values ? (r >> 1) : r, grp = values ? (r & 1) : 0;
       const int j = pos >> 3, slot = (pos >> 2) & 1, tt = pos & 3;
@@ -462,8 +363,8 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
       // head t's scale sits in the lanes that fold for head t (g = 2t)
       qs = __shfl_sync(0xffffffffu, up, 8 * t) * p.scaling * LOG2E;
     }
-    const bool dense = tile >= s.k_groups;
-    const int tok0 = dense ? (tile - s.k_groups) * DT : tile * G;
+    const bool dense = tile >= kt;
+    const int tok0 = dense ? (tile - kt) * DT : tile * G;
     const int ntok = dense ? min(DT, s.res_len - tok0) : G;
     const long long mask0 = p.mask ? b * p.mask_stride_b + (dense ? nq : 0) + tok0 : 0;
 
@@ -728,7 +629,7 @@ int g_window_base[kMaxDevices];      // 0 = not probed yet, -1 = probe failed, e
 // memory).  The tensor-core kernel addresses its buffers absolutely (the lookup table must sit at 65536),
 // so the planner needs the number; it is measured once per device with a one-thread kernel and a
 // synchronous 4-byte read of a device variable, no allocation.
-static int window_base() {
+int mz_smem_window_base() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= mzm::kMaxDevices) return -1;
   std::lock_guard<std::mutex> lk(mzm::g_mu);
@@ -754,7 +655,7 @@ bool mz_decode_mma_supported(const MzDecodeParams& p) {
   if (p.gqa != 1 && p.gqa != 2 && p.gqa != 4) return false;
   // the residual-tile path reads the query in 4-byte pieces
   if (((uintptr_t)p.query & 3) || ((p.q_stride_b | p.q_stride_h) & 1)) return false;
-  return window_base() > 0;
+  return mz_smem_window_base() > 0;
 }
 
 int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots) {
@@ -766,7 +667,7 @@ int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slo
   if (sb < (unsigned)mzm::DENSE_BYTES) sb = mzm::DENSE_BYTES;
   sb = (sb + 127u) & ~127u;
   const unsigned table_bytes = (1u << (2 * s.bits)) * 256u;
-  const unsigned wb = (unsigned)window_base();
+  const unsigned wb = (unsigned)mz_smem_window_base();
   const unsigned low_base = (wb + 127u) & ~127u;
   const unsigned high_base = mzm::TBL + table_bytes;
   const unsigned per_low = sb + mzm::A_BYTES;

@@ -563,40 +563,58 @@ __global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_t
 // WIDE (many records per pair, few pairs): one CTA per (pair, head); its four warp-quads each merge every
 // fourth chunk of records and the four partial states are merged in a fixed order at the end.
 constexpr int kMaxCombineSlots = 4096;
+// The workers of plan `tp` that can hold records of `pair` lie in [first, last] (a superset; see above).
+struct WorkerRange { long long first, last; };
+__device__ __forceinline__ WorkerRange candidate_workers(const MzTilesPlan& tp, int pair) {
+  WorkerRange r = {0, -1};
+  if (tp.total_warps <= 0) return r;
+  const unsigned quot = tp.cost_quot ? tp.cost_quot : 1u;
+  const unsigned c_lo = (unsigned)pair * (unsigned)tp.pair_cost, c_hi = c_lo + (unsigned)tp.pair_cost;
+  r.first = (long long)(c_lo / (quot + 1u)) - 1;
+  r.last = (long long)((c_hi - 1u) / quot) + 1;
+  if (r.first < 0 || tp.cost_quot == 0) r.first = 0;
+  if (r.last > tp.total_warps - 1 || tp.cost_quot == 0) r.last = tp.total_warps - 1;   // more workers than cost units: test them all
+  return r;
+}
+// record index of worker gw's segment for `pair` (first_record = index of the plan's first record), or -1
+__device__ __forceinline__ long long record_of(const MzTilesPlan& tp, long long gw, int pair, long long first_record) {
+  const int T = tp.tiles_per_pair;
+  const long long lo = (long long)pair * T, hi = lo + T;
+  long long f0, f1;
+  mz_warp_tiles(tp, gw, &f0, &f1);
+  if (!(f0 < hi && f1 > lo && f0 < f1)) return -1;
+  return first_record + gw * tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T));
+}
 template <bool WIDE>
 __global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
-  __shared__ int s_slot[kMaxCombineSlots];     // record slot of candidate i, or -1
+  __shared__ int s_slot[kMaxCombineSlots];     // record of candidate i, or -1
   __shared__ float s_part[WIDE ? 4 : 1][WIDE ? 130 : 1];
   const int pair = WIDE ? blockIdx.x / p.gqa : blockIdx.x;
-  const int W = p.tp.total_warps, T = p.tp.tiles_per_pair, gqa = p.gqa;
-  const long long lo = (long long)pair * T, hi = lo + T;
-  const unsigned quot = p.tp.cost_quot ? p.tp.cost_quot : 1u;
-  const unsigned c_lo = (unsigned)pair * (unsigned)p.tp.pair_cost, c_hi = c_lo + (unsigned)p.tp.pair_cost;
-  long long g_first = (long long)(c_lo / (quot + 1u)) - 1, g_last = (long long)((c_hi - 1u) / quot) + 1;
-  if (g_first < 0 || p.tp.cost_quot == 0) g_first = 0;
-  if (g_last > W - 1 || p.tp.cost_quot == 0) g_last = W - 1;     // more warps than cost units: no bound, test them all
-  const long long cand = g_last - g_first + 1;
-  const bool listed = cand <= kMaxCombineSlots && (long long)W * p.tp.max_segs < (1LL << 31);
+  const int gqa = p.gqa;
+  // candidates of the main plan, then of the residual-tile plan of the tcgen05 route (its records follow)
+  const WorkerRange ra = candidate_workers(p.tp, pair), rb = candidate_workers(p.tp2, pair);
+  const long long cand_a = ra.last - ra.first + 1, cand_b = rb.last - rb.first + 1;
+  const long long cand = cand_a + cand_b;
+  const long long first_b = p.slots_a / gqa;
+  const bool listed = cand <= kMaxCombineSlots &&
+                      first_b + (long long)p.tp.total_warps * p.tp.max_segs + (long long)p.tp2.total_warps * p.tp2.max_segs < (1LL << 31);
   if (listed) {
-    for (int i = threadIdx.x; i < cand; i += blockDim.x) {
-      long long f0, f1;
-      mz_warp_tiles(p.tp, g_first + i, &f0, &f1);
-      const bool on = f0 < hi && f1 > lo && f0 < f1;
-      s_slot[i] = on ? (int)((g_first + i) * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T))) : -1;
-    }
+    for (int i = threadIdx.x; i < cand; i += blockDim.x)
+      s_slot[i] = (int)(i < cand_a ? record_of(p.tp, ra.first + i, pair, 0) : record_of(p.tp2, rb.first + (i - cand_a), pair, first_b));
   }
-  // everything above is arithmetic on the plan; the records themselves are the main kernel's output
+  // everything above is arithmetic on the plans; the records themselves are the main kernels' output
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncthreads();
   const int n = (int)cand;
   // more candidates than the list holds (a huge explicit split count): every thread walks them itself
   auto for_each_slot = [&](auto&& fn) {
-    for (long long gw = g_first; gw <= g_last; ++gw) {
-      long long f0, f1;
-      mz_warp_tiles(p.tp, gw, &f0, &f1);
-      if (f0 >= hi) break;
-      if (f1 <= lo || f0 >= f1) continue;
-      fn(gw * p.tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T)));
+    for (long long gw = ra.first; gw <= ra.last; ++gw) {
+      const long long rec = record_of(p.tp, gw, pair, 0);
+      if (rec >= 0) fn(rec);
+    }
+    for (long long gw = rb.first; gw <= rb.last; ++gw) {
+      const long long rec = record_of(p.tp2, gw, pair, first_b);
+      if (rec >= 0) fn(rec);
     }
   };
   const int quad = threadIdx.x >> 7, quads = blockDim.x >> 7;

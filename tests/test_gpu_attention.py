@@ -255,3 +255,28 @@ def test_many_pairs_and_split_counts_beyond_16_bits(oracle):
     for splits in (3, 17, 3000):          # 24 * 3000 = 72,000 warps
         again = decode_attention(layer, q.cuda(), 0.09, out_dtype=torch.float32, splits=splits)
         assert (again - got).abs().max().item() < SPLIT_TOL, splits
+
+
+@pytest.mark.parametrize("which,name", [(1, "generic"), (2, "tiles"), (3, "mma"), (4, "umma")])
+def test_every_kernel_against_the_oracle(oracle, which, name):
+    """The four decode kernels on the same caches (4- and 2-bit, group 64, a pair boundary inside a worker's range,
+    an odd number of tiles, a mask): each within 2e-3 of the oracle.  `umma` is the tcgen05 / tensor-memory kernel,
+    which the automatic selection does not use yet."""
+    from muzero_b200.cache.attention import decode_attention
+    from muzero_b200.kernels._cabi import load_library
+    lib = load_library()
+    before = lib.mz_debug_force_kernel(which)
+    try:
+        for bits, S, steps in ((4, 1000, 3), (2, 600, 70)):
+            ref, layer, q = _oracle_and_gpu_layers(oracle, 3, 2, 8, S, 128, bits, 64, 128, seed=900 + bits, steps=steps)
+            total = S + steps
+            mask = torch.zeros(3, 1, 1, total)
+            mask[1, ..., 100:260] = -3.0
+            mask[2, ..., :33] = torch.finfo(torch.bfloat16).min
+            for m in (None, mask):
+                want = oracle.decode_attention_oracle(q, ref, 0.09, 4, mask=m, compute_dtype=torch.float32)
+                got = decode_attention(layer, q.cuda(), 0.09, None if m is None else m.cuda(), out_dtype=torch.float32)
+                err = (got.cpu() - want).abs().max().item()
+                assert err <= TOL, (name, bits, m is not None, err)
+    finally:
+        lib.mz_debug_force_kernel(before)
