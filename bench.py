@@ -1,6 +1,7 @@
 """Benchmark of the KV-cache hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --impl reference-gpu      # context: the unmodified reference's own CUDA path on this GPU
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Workload (BASELINE config 1 shape, one decode step of the hot path for a Qwen3-8B shaped
@@ -599,12 +600,85 @@ def run_reference(args) -> dict:
     }
 
 
+def run_reference_gpu(args) -> dict:
+    """Context, not the reference arm the run is graded on: the UNMODIFIED reference package, installed under
+    baseline/_ref (git-ignored), driven on cuda:0 through its own API - MuZeroCacheLayer.update() and
+    mu_zero_decode_attention_forward() - on the same shape and synthetic data as `run_ours`, with its own JIT-built
+    CUDA extension.  Two of its paths are timed: the stock decode path (qk kernel, softmax, av kernel, dense residual
+    matmuls) and the fused chunked prefix decode it enables with MUZERO_FUSED_PREFIX_DECODE=1.  `--layers` distinct
+    caches are walked per step (default 8 here: 2 GB of codes, larger than L2) and the per-layer time is scaled to 36."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "muzero")):
+        return {"impl": "reference-gpu", "unavailable": "baseline/_ref holds no reference install"}
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(ref_dir, "_ext"))
+    sys.path.insert(0, ref_dir)                      # ahead of the repo root, whose `muzero` is this package's alias
+    import muzero as ref
+    assert os.path.abspath(ref.__file__).startswith(ref_dir), ref.__file__
+    from muzero.cache.attention import mu_zero_decode_attention_forward as ref_forward
+    from muzero.cache.layer import MuZeroCacheLayer as RefLayer
+    from types import SimpleNamespace
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    bits, L, B = args.bits, min(args.layers, 8), args.batch
+    gen = torch.Generator(device=device).manual_seed(1234)
+    chan = torch.exp(torch.randn(D, device=device, generator=gen))
+    layers = []
+    try:
+        for _ in range(L):
+            layer = RefLayer(ref.MuZeroConfig(bits=bits, q_group_size=GROUP, residual_length=RES, alpha_key=2.0, alpha_value=2.0))
+            k = (torch.randn(B, KVH, CTX + RES, D, device=device, generator=gen) * chan).to(torch.bfloat16)
+            v = torch.randn(B, KVH, CTX + RES, D, device=device, generator=gen).to(torch.bfloat16)
+            layer.update(k, v, {"materialize_full_kv": False})
+            del k, v
+            layers.append(layer)
+        q = torch.randn(B, QH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+        k_new = torch.randn(B, KVH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+        v_new = torch.randn(B, KVH, 1, D, device=device, generator=gen).to(torch.bfloat16)
+        module = SimpleNamespace(num_key_value_groups=QH // KVH)
+
+        def step(with_update: bool):
+            for layer in layers:
+                if with_update:
+                    layer.update(k_new, v_new, {"materialize_full_kv": False})
+                out = ref_forward(module, q, None, D ** -0.5, layer.get_attention_state())
+                if out is None:
+                    raise RuntimeError("the reference's decode forward declined the call")
+
+        def timed(with_update: bool, steps: int) -> float:
+            for _ in range(3):
+                step(with_update)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                step(with_update)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / (steps * L)       # us per layer
+
+        res = {}
+        for name, flag in (("stock", "0"), ("fused_chunked", "1")):
+            os.environ["MUZERO_FUSED_PREFIX_DECODE"] = flag
+            ref.reset_mu_zero_decode_stats()
+            res[name] = {"attention_us_per_layer": timed(False, args.steps), "step_us_per_layer": timed(True, args.steps),
+                         "decode_stats": {k: v for k, v in ref.get_mu_zero_decode_stats().items() if v}}
+    except Exception as exc:                                  # a build or launch failure of the reference is the result
+        return {"impl": "reference-gpu", "unavailable": f"{type(exc).__name__}: {str(exc)[-400:]}"}
+    best = min(res.values(), key=lambda r: r["step_us_per_layer"])
+    ms_step = best["step_us_per_layer"] * LAYERS / 1e3
+    return {"impl": "reference-gpu", "metric": METRIC, "value": B / (ms_step / 1e3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": ms_step, "higher_is_better": True,
+            "dtype": f"u{bits} codes, fp16 metadata, bf16 residual", "data": "synthetic", "extrapolated": True,
+            "config": workload_config(bits, L, B, 1, CTX + RES), "paths": res,
+            "note": "the reference's own CUDA extension and torch ops on this GPU; per-layer time of the faster path scaled to 36 layers"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--batch", type=int, default=BATCH)
@@ -629,6 +703,9 @@ def main():
         out = run_kv_split(args)
         if out:
             print(json.dumps(out))
+        return
+    if args.impl == "reference-gpu":
+        print(json.dumps(run_reference_gpu(args)))
         return
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out:

@@ -181,6 +181,16 @@ typedef struct mz_decode_args {
  */
 int mz_debug_force_kernel(int which);
 
+/*
+ * Testing aid of the checked build (library compiled with -DMZ_BOUNDS): the number of guarded global
+ * accesses on the current device that fell outside the extent the host passed and were skipped; the
+ * index, extent and site number of the first one go to the optional pointers; `reset` != 0 clears the
+ * record.  Synchronizes the device.  Returns -1 from a library built without the flag, -2 when the
+ * record cannot be read.  Every entry point also opens an NVTX range named after itself.  No counterpart
+ * in the reference, whose kernels carry no bounds assertions (muzero/kernels/loader.py).
+ */
+long long mz_bounds_violations(long long* first_index, long long* first_extent, int* first_site, int reset);
+
 /* Bytes of workspace mz_decode_attention needs for these arguments (splits resolved as the call would). */
 size_t mz_decode_workspace_bytes(const mz_decode_args* args);
 

@@ -35,6 +35,36 @@ int mz_fail(int code, const char* fmt, ...);
       return mz_fail(MZ_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// ---------------------------------------------------------------------------
+// NVTX range around an entry point: named in Nsight timelines, a few ns when no tool is attached.
+// ---------------------------------------------------------------------------
+#include <nvtx3/nvToolsExt.h>
+struct MzRange {
+  explicit MzRange(const char* name) { nvtxRangePushA(name); }
+  ~MzRange() { nvtxRangePop(); }
+  MzRange(const MzRange&) = delete;
+  MzRange& operator=(const MzRange&) = delete;
+};
+#define MZ_RANGE(name) MzRange mz_range__(name)
+
+// ---------------------------------------------------------------------------
+// checked build (-DMZ_BOUNDS): every guarded global access compares its element index with the extent the
+// host passed; an access outside is SKIPPED and counted (first offender kept), never trapped, so the context
+// stays usable and mz_bounds_violations() reports it.  Without the flag the guard compiles to `true`.
+// ---------------------------------------------------------------------------
+#ifdef MZ_BOUNDS
+struct MzBoundsRecord { unsigned long long count; long long index; long long extent; int site; int pad; };
+extern __device__ MzBoundsRecord g_mz_bounds;
+__device__ __forceinline__ bool mz_in_bounds(long long i, long long n, int site) {
+  if (i >= 0 && i < n) return true;
+  if (atomicAdd(&g_mz_bounds.count, 1ull) == 0) { g_mz_bounds.index = i; g_mz_bounds.extent = n; g_mz_bounds.site = site; }
+  return false;
+}
+#define MZ_IN_BOUNDS(i, n, site) mz_in_bounds((long long)(i), (long long)(n), (site))
+#else
+#define MZ_IN_BOUNDS(i, n, site) true
+#endif
+
 static inline int mz_dtype_size(int dt) { return dt == MZ_F32 ? 4 : 2; }
 static inline bool mz_dtype_ok(int dt) { return dt == MZ_F32 || dt == MZ_F16 || dt == MZ_BF16; }
 static inline int mz_row_bytes(int group, int bits) { return (group * bits + 7) / 8; }

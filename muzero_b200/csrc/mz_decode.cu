@@ -153,6 +153,7 @@ int launch_partials(const mz_decode_args* a, Plan* plan, cudaStream_t st) {
   p.part.m = (float*)a->workspace;
   p.part.l = p.part.m + plan->slots;
   p.part.acc = p.part.l + plan->slots;
+  p.part.slots = (long long)plan->slots;
   if (!plan->tiles) return mz_launch_decode_generic(p, st);
   if (p.tp.kind == 2) return mz_launch_decode_umma(p, st);
   return p.tp.kind == 1 ? mz_launch_decode_mma(p, st) : mz_launch_decode_tiles(p, st);
@@ -231,6 +232,7 @@ extern "C" size_t mz_decode_workspace_bytes(const mz_decode_args* args) {
 }
 
 extern "C" int mz_decode_attention(const mz_decode_args* a, void* stream) {
+  MZ_RANGE("mz_decode_attention");
   Plan plan;
   cudaStream_t st = (cudaStream_t)stream;
   MZ_REQUIRE(a != nullptr && a->out != nullptr && mz_dtype_ok(a->out_dtype), "bad output");
@@ -241,6 +243,7 @@ extern "C" int mz_decode_attention(const mz_decode_args* a, void* stream) {
 }
 
 extern "C" int mz_decode_attention_partial(const mz_decode_args* a, float* m, float* l, float* acc, void* stream) {
+  MZ_RANGE("mz_decode_attention_partial");
   Plan plan;
   cudaStream_t st = (cudaStream_t)stream;
   MZ_REQUIRE(m && l && acc, "NULL partial output");
@@ -251,6 +254,7 @@ extern "C" int mz_decode_attention_partial(const mz_decode_args* a, float* m, fl
 }
 
 extern "C" int mz_decode_attention_partial_packed(const mz_decode_args* a, float* records, void* stream) {
+  MZ_RANGE("mz_decode_attention_partial_packed");
   Plan plan;
   cudaStream_t st = (cudaStream_t)stream;
   MZ_REQUIRE(records != nullptr, "NULL partial output");
@@ -277,12 +281,14 @@ int merge_launch(const PartialView& v, int n_parts, long long rows, int head_dim
 
 extern "C" int mz_lse_merge(const float* m, const float* l, const float* acc, int n_parts, long long rows, int head_dim, void* out,
                             int out_dtype, void* stream) {
+  MZ_RANGE("mz_lse_merge");
   const PartialView v = {m, l, acc, 1, rows, head_dim, rows * head_dim};
   return merge_launch(v, n_parts, rows, head_dim, out, out_dtype, stream);
 }
 
 extern "C" int mz_lse_merge_packed(const float* records, int n_parts, long long rows, int head_dim, void* out, int out_dtype,
                                    void* stream) {
+  MZ_RANGE("mz_lse_merge_packed");
   MZ_REQUIRE(records != nullptr, "NULL pointer");
   const long long rec = head_dim + 2;
   const PartialView v = {records + head_dim, records + head_dim + 1, records, rec, rows * rec, rec, rows * rec};

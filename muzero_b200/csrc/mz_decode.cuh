@@ -11,6 +11,7 @@ struct MzPartials {
   float* m;
   float* l;
   float* acc;  // [slots][D]
+  long long slots;   // records the three arrays hold (read by the checked build only)
 };
 
 // Work decomposition of the tiled kernel: the flat list of (pair, tile) items, pair = b*KVH+kvh,

@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(THREADS) decode_generic_kernel(const MzDecodeP
   // ---- partial out
   for (int hh = 0; hh < gqa; ++hh) {
     const long long slot = ((long long)b * p.H + kvh * gqa + hh) * p.splits + split;
-    if (tid == 0) { p.part.m[slot] = m_s[hh]; p.part.l[slot] = l_s[hh]; }
+    if (tid == 0 && MZ_IN_BOUNDS(slot, p.part.slots, 13)) { p.part.m[slot] = m_s[hh]; p.part.l[slot] = l_s[hh]; }
   }
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(THREADS) decode_generic_kernel(const MzDecodeP
       for (int hh = 0; hh < MAX_GQA; ++hh) {
         if (hh < gqa) {
           const long long slot = ((long long)b * p.H + kvh * gqa + hh) * p.splits + split;
-          p.part.acc[slot * D + d] = acc[hh][j];
+          if (MZ_IN_BOUNDS(slot, p.part.slots, 14)) p.part.acc[slot * D + d] = acc[hh][j];
         }
       }
     }

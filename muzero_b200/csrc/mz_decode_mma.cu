@@ -282,6 +282,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
     }
     if (t < GQA) {
       const long long slot = ((long long)gw * p.tp.max_segs + seg) * GQA + t;
+      if (!MZ_IN_BOUNDS(slot, p.part.slots, 10)) return;
       float* dst = p.part.acc + slot * D + 8 * g;
       float4 v;
       v = make_float4(out[0][0] + out[0][1] + b0, out[0][2] + out[0][3] + b0, out[1][0] + out[1][1] + b0, out[1][2] + out[1][3] + b0);

@@ -35,6 +35,7 @@ int scratch_address(void** out) {
 }  // namespace
 
 extern "C" int mz_decode_attention_static(const mz_decode_args* args, void* stream) {
+  MZ_RANGE("mz_decode_attention_static");
   MZ_REQUIRE(args != nullptr, "args is NULL");
   size_t need = 0;
   int needs_tables = 0;

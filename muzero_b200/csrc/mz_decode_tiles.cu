@@ -260,6 +260,7 @@ __global__ void __launch_bounds__(Cfg<BITS, G, GQA>::MAX_WARPS * 32, 1) decode_t
   };
   auto write_partial = [&]() {
     const long long slot0 = ((long long)gw * p.tp.max_segs + seg) * GQA;
+    if (!MZ_IN_BOUNDS(slot0 + GQA - 1, p.part.slots, 11)) return;
 #pragma unroll
     for (int h = 0; h < GQA; ++h) {
       float2 t[4];

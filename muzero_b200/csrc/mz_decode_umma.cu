@@ -259,13 +259,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_umma_kernel(const MzDecodeP
     // TMEM lane 16h' + 8r + g' of this warp holds channel 32w + 4g' + 2h' + r
     const int chan = 32 * w + 4 * (lane & 7) + 2 * (lane >> 4) + ((lane >> 3) & 1);
     const long long slot0 = ((long long)gwg * p.tp.max_segs + seg) * GQA;
+    const bool in_range = MZ_IN_BOUNDS(slot0 + GQA - 1, p.part.slots, 12);   // always true outside the checked build
 #pragma unroll
-    for (int h = 0; h < GQA; ++h) {
+    for (int h = 0; h < GQA && in_range; ++h) {
       const float bs = ldsf(r_base + ((0 * 2 + grp) * 4 + h) * 4) + ldsf(r_base + ((1 * 2 + grp) * 4 + h) * 4) +
                        ldsf(r_base + ((2 * 2 + grp) * 4 + h) * 4) + ldsf(r_base + ((3 * 2 + grp) * 4 + h) * 4);
       p.part.acc[(slot0 + h) * D + chan] = __uint_as_float(v[2 * h]) + __uint_as_float(v[2 * h + 1]) + bs;
     }
-    if (tid < GQA) {
+    if (tid < GQA && in_range) {
       const float lt = ldsf(r_l + (0 * 4 + tid) * 4) + ldsf(r_l + (1 * 4 + tid) * 4) + ldsf(r_l + (2 * 4 + tid) * 4) + ldsf(r_l + (3 * 4 + tid) * 4);
       float mv = -INFINITY;
 #pragma unroll
@@ -672,6 +673,7 @@ int mz_launch_decode_umma(const MzDecodeParams& p, cudaStream_t st) {
     q.part.m = p.part.m + p.slots_a;
     q.part.l = p.part.l + p.slots_a;
     q.part.acc = p.part.acc + p.slots_a * p.s.head_dim;
+    q.part.slots = p.part.slots - (long long)p.slots_a;
     int rc = mz_launch_decode_mma(q, st);
     if (rc) return rc;
   }

@@ -48,6 +48,9 @@ __device__ void flush_key_tile(const FlushParams& p, uint16_t* tile) {
   const int grp = s.k_groups + j;
   uint8_t* dst_rows = s.packed_k + b * s.pk_stride_b + h * s.pk_stride_h + (long long)grp * D * p.QB;
   const long long meta0 = b * s.km_stride_b + h * s.km_stride_h + (long long)grp * D;
+  // checked build: the last byte of this group's rows and its last metadata element lie inside the pair's slab
+  if (!MZ_IN_BOUNDS((long long)(grp + 1) * D * p.QB - 1, s.pk_stride_h, 1) ||
+      !MZ_IN_BOUNDS((long long)(grp + 1) * D - 1, s.km_stride_h, 2)) return;
   // A channel's G tokens are split over `parts` threads when the CTA has more threads than channels (2 for
   // head_dim 128 and 256 threads): partial min/max meet in shared memory, then each thread quantizes and packs
   // its own share of the row (whole octets, so the byte ranges of the parts do not overlap).
@@ -140,6 +143,7 @@ __device__ void flush_value_rows_fast(const FlushParams& p) {
   for (int i = 0; i < 8; ++i) word |= ((unsigned long long)q.code(v[i])) << (i * s.bits);
   const long long tok = s.v_tokens + t;
   uint8_t* dst = s.packed_v + b * s.pv_stride_b + h * s.pv_stride_h + (tok * p.NG + grp) * p.QB + sub * s.bits;
+  if (!MZ_IN_BOUNDS((tok * p.NG + grp + 1) * p.QB - 1, s.pv_stride_h, 3) || !MZ_IN_BOUNDS(tok * p.NG + grp, s.vm_stride_h, 4)) return;
   mz_store_octet(dst, word, s.bits);
   if (sub == 0) {
     const long long m = b * s.vm_stride_b + h * s.vm_stride_h + tok * p.NG + grp;
@@ -177,6 +181,7 @@ __device__ void flush_value_rows_generic(const FlushParams& p) {
   q.setup(mn, mx, s.bits, s.alpha_value, p.eps, p.ctab_v, p.ctab_v_n);
   const long long tok = s.v_tokens + t;
   uint8_t* dst = s.packed_v + b * s.pv_stride_b + h * s.pv_stride_h + (tok * p.NG + grp) * p.QB;
+  if (!MZ_IN_BOUNDS((tok * p.NG + grp + 1) * p.QB - 1, s.pv_stride_h, 5) || !MZ_IN_BOUNDS(tok * p.NG + grp, s.vm_stride_h, 6)) return;
   for (int byte = lane; byte < p.QB; byte += 32) {
     uint32_t out = 0;
     const int first = (byte * 8) / s.bits, last = min(G - 1, (byte * 8 + 7) / s.bits);
@@ -271,6 +276,7 @@ bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
 extern "C" int mz_flush_kv_parts(const mz_kv_store* s, int n_key_tokens, int value_first, int n_value_tokens, float eps,
                                  void* stream) {
+  MZ_RANGE("mz_flush_kv_parts");
   int rc = mz_check_store_basic(s);
   if (rc) return rc;
   if ((rc = mz_check_store_quantized(s))) return rc;
@@ -315,6 +321,7 @@ extern "C" int mz_flush_kv(const mz_kv_store* s, int n_tokens, float eps, void* 
 }
 
 extern "C" int mz_append_kv(const mz_kv_store* s, const void* k_new, const void* v_new, long long nsb, long long nsh, void* stream) {
+  MZ_RANGE("mz_append_kv");
   int rc = mz_check_store_basic(s);
   if (rc) return rc;
   if ((rc = mz_check_store_residual(s))) return rc;
@@ -327,6 +334,7 @@ extern "C" int mz_append_kv(const mz_kv_store* s, const void* k_new, const void*
 
 extern "C" int mz_dequantize_kv(const mz_kv_store* s, int g0, int g1, void* out_k, int t0, int t1, void* out_v, int out_dtype,
                                 float eps, void* stream) {
+  MZ_RANGE("mz_dequantize_kv");
   int rc = mz_check_store_basic(s);
   if (rc) return rc;
   if ((rc = mz_check_store_quantized(s))) return rc;

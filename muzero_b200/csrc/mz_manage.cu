@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(256) gather_batch_kernel(const GatherParams p)
 // zeroed by the caller) is set to 1 if an index was out of range.
 extern "C" int mz_store_gather_batch(const mz_kv_store* src, const mz_kv_store* dst, const long long* index, int* status,
                                      void* stream) {
+  MZ_RANGE("mz_store_gather_batch");
   int rc = mz_check_store_basic(src);
   if (rc) return rc;
   if ((rc = mz_check_store_basic(dst))) return rc;

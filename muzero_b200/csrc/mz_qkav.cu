@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(256) av_output_kernel(const mz_kv_store s, con
 
 extern "C" int mz_qk_logits(const mz_kv_store* s, const void* query, long long qsb, long long qsh, int q_heads, float scaling,
                             void* out, int out_dtype, void* stream) {
+  MZ_RANGE("mz_qk_logits");
   int rc = mz_check_store_basic(s);
   if (rc) return rc;
   if ((rc = mz_check_store_quantized(s))) return rc;
@@ -93,6 +94,7 @@ extern "C" int mz_qk_logits(const mz_kv_store* s, const void* query, long long q
 
 extern "C" int mz_av_output(const mz_kv_store* s, const void* weights, int w_dtype, int n_tokens, int q_heads, void* out,
                             int out_dtype, void* stream) {
+  MZ_RANGE("mz_av_output");
   int rc = mz_check_store_basic(s);
   if (rc) return rc;
   if ((rc = mz_check_store_quantized(s))) return rc;

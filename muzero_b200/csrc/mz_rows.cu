@@ -151,6 +151,7 @@ int launch_quantize(const void* x, long long n_rows, int group, int bits, float 
 
 extern "C" int mz_quantize_rows(const void* x, int x_dtype, long long n_rows, int group, int bits, float alpha, float eps,
                                 uint8_t* packed, void* mn, void* scale, int meta_dtype, void* stream) {
+  MZ_RANGE("mz_quantize_rows");
   MZ_REQUIRE(mz_dtype_ok(x_dtype) && mz_dtype_ok(meta_dtype), "bad dtype code");
   MZ_REQUIRE(bits >= 1 && bits <= 8, "bits must be 1..8, got %d", bits);
   MZ_REQUIRE(group > 0 && n_rows >= 0, "bad shape: n_rows=%lld group=%d", n_rows, group);
@@ -168,6 +169,7 @@ extern "C" int mz_quantize_rows(const void* x, int x_dtype, long long n_rows, in
 
 extern "C" int mz_dequantize_rows(const uint8_t* packed, const void* mn, const void* scale, int meta_dtype, long long n_rows,
                                   int group, int bits, float alpha, float eps, void* out, int out_dtype, void* stream) {
+  MZ_RANGE("mz_dequantize_rows");
   MZ_REQUIRE(mz_dtype_ok(out_dtype) && mz_dtype_ok(meta_dtype), "bad dtype code");
   MZ_REQUIRE(bits >= 1 && bits <= 8, "bits must be 1..8, got %d", bits);
   MZ_REQUIRE(group > 0 && n_rows >= 0, "bad shape: n_rows=%lld group=%d", n_rows, group);

@@ -30,6 +30,7 @@ extern "C" size_t mz_decode_step_workspace_bytes(const mz_decode_args* a, int re
 extern "C" int mz_decode_step(mz_decode_args* a, const void* k_new, const void* v_new, long long new_stride_b,
                               long long new_stride_h, int residual_length, int flush_unit, int group_capacity,
                               int window_capacity, float eps, void* stream) {
+  MZ_RANGE("mz_decode_step");
   MZ_REQUIRE(a != nullptr, "args is NULL");
   mz_kv_store* s = &a->store;
   MZ_REQUIRE(s->group > 0 && residual_length >= 0, "bad group %d / residual_length %d", s->group, residual_length);

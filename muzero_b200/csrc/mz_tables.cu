@@ -27,6 +27,31 @@ extern "C" int mz_last_error(char* buf, int len) {
   return (int)strlen(buf);
 }
 
+// Checked build: the record the guarded accesses write (current device).  Synchronizes the device.
+#ifdef MZ_BOUNDS
+__device__ MzBoundsRecord g_mz_bounds = {0ull, 0ll, 0ll, 0, 0};
+#endif
+extern "C" long long mz_bounds_violations(long long* first_index, long long* first_extent, int* first_site, int reset) {
+#ifdef MZ_BOUNDS
+  MzBoundsRecord r;
+  if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpyFromSymbol(&r, g_mz_bounds, sizeof(r)) != cudaSuccess) {
+    mz_fail(MZ_ERR_CUDA, "reading the bounds record failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return -2;
+  }
+  if (first_index) *first_index = r.index;
+  if (first_extent) *first_extent = r.extent;
+  if (first_site) *first_site = r.site;
+  if (reset) {
+    const MzBoundsRecord zero = {0ull, 0ll, 0ll, 0, 0};
+    cudaMemcpyToSymbol(g_mz_bounds, &zero, sizeof(zero));
+  }
+  return (long long)r.count;
+#else
+  (void)first_index; (void)first_extent; (void)first_site; (void)reset;
+  return -1;   // not a checked build
+#endif
+}
+
 // ---------------------------------------------------------------------------
 namespace {
 std::mutex g_mu;

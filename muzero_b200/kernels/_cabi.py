@@ -22,7 +22,7 @@ EXPORTS = (
     "mz_version", "mz_last_error", "mz_set_expand_table", "mz_quantize_rows", "mz_dequantize_rows",
     "mz_flush_kv", "mz_append_kv", "mz_dequantize_kv", "mz_decode_workspace_bytes", "mz_decode_attention",
     "mz_decode_attention_partial", "mz_lse_merge", "mz_qk_logits", "mz_av_output", "mz_decode_attention_static",
-    "mz_decode_step", "mz_decode_step_workspace_bytes", "mz_flush_kv_parts", "mz_decode_workspace_bound", "mz_decode_attention_partial_packed", "mz_lse_merge_packed", "mz_store_gather_batch", "mz_debug_force_kernel",
+    "mz_decode_step", "mz_decode_step_workspace_bytes", "mz_flush_kv_parts", "mz_decode_workspace_bound", "mz_decode_attention_partial_packed", "mz_lse_merge_packed", "mz_store_gather_batch", "mz_debug_force_kernel", "mz_bounds_violations",
 )
 
 
@@ -108,6 +108,8 @@ def load_library() -> ctypes.CDLL:
     lib.mz_store_gather_batch.argtypes = [POINTER(KVStore), POINTER(KVStore), c_void_p, c_void_p, c_void_p]
     lib.mz_debug_force_kernel.argtypes = [c_int]
     lib.mz_debug_force_kernel.restype = c_int
+    lib.mz_bounds_violations.argtypes = [ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(c_int), c_int]
+    lib.mz_bounds_violations.restype = ctypes.c_longlong
     lib.mz_qk_logits.argtypes = [POINTER(KVStore), c_void_p, c_longlong, c_longlong, c_int, c_float, c_void_p, c_int, c_void_p]
     lib.mz_av_output.argtypes = [POINTER(KVStore), c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
     _lib = lib

@@ -12,7 +12,7 @@ from conftest import ROOT
 def test_library_exports_every_declared_symbol():
     from muzero_b200.kernels import _cabi
     header = open(os.path.join(ROOT, "include", "muzero_b200.h")).read()
-    declared = set(re.findall(r"^\s*(?:int|size_t)\s+(mz_\w+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^\s*(?:int|size_t|long long)\s+(mz_\w+)\s*\(", header, flags=re.M))
     assert declared == set(_cabi.EXPORTS), declared ^ set(_cabi.EXPORTS)
     lib = _cabi.load_library()
     for name in declared:
