@@ -475,8 +475,17 @@ def run_generate(args) -> dict:
     """BASELINE config 2 (secondary workload): greedy `generate()` on a random-init (std 0.02)
     Qwen3-8B-architecture decoder in bf16 through `patch_transformers()` and
     `cache_implementation="mu_zero_{bits}bit"`; decode-only tokens/s (prefill excluded, as the
-    reference's throughput bench does).  `--cache dynamic` runs stock transformers for context."""
+    reference's throughput bench does).  `--cache dynamic` runs stock transformers for context;
+    `--impl reference-gpu` runs the unmodified reference package from baseline/_ref instead of this one."""
+    ours = args.impl != "reference-gpu"
+    if not ours:
+        ref_dir = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref_dir, "muzero")):
+            return {"impl": "reference-gpu", "unavailable": "baseline/_ref holds no reference install"}
+        os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(ref_dir, "_ext"))
+        sys.path.insert(0, ref_dir)                  # ahead of the repo root, whose `muzero` is this package's alias
     import muzero
+    assert ours or os.path.abspath(muzero.__file__).startswith(os.path.join(ROOT, "baseline")), muzero.__file__
     from transformers import Qwen3Config, Qwen3ForCausalLM
     from transformers.generation.streamers import BaseStreamer
     muzero.patch_transformers()
@@ -510,7 +519,7 @@ def run_generate(args) -> dict:
                       cache_config={"q_group_size": GROUP, "residual_length": RES, "backend": "cuda"})
     clock = Clock()
     grabbed = []          # the cache object generate() builds, for the cache-bytes columns
-    if args.cache == "mu_zero":
+    if args.cache == "mu_zero" and ours:
         from muzero_b200.integrations import transformers_patch as tp
         real_init = tp.MuZeroCache.__init__
         def grabbing_init(self, *a, **kw):
@@ -521,7 +530,7 @@ def run_generate(args) -> dict:
     torch.cuda.reset_peak_memory_stats()
     with torch.no_grad():
         out = model.generate(input_ids=ids, attention_mask=torch.ones_like(ids), streamer=clock, **kwargs)
-    if args.cache == "mu_zero":
+    if args.cache == "mu_zero" and ours:
         tp.MuZeroCache.__init__ = real_init
     # stamps[0] = prompt echo, stamps[1] = first new token (end of prefill); decode = the rest
     t = clock.stamps
@@ -539,7 +548,7 @@ def run_generate(args) -> dict:
             resid += mb(layer._value_buffer if layer._value_buffer is not None else layer.values)
         cache_mb = {"cache_packed_mb": packed, "cache_meta_mb": meta, "cache_residual_mb": resid,
                     "cache_total_mb": packed + meta + resid}
-    return {**cache_mb, "mode": "generate", "cache": args.cache, "bits": args.bits, "layers": args.layers, "batch": args.batch,
+    return {**cache_mb, "mode": "generate", "impl": args.impl, "cache": args.cache, "bits": args.bits, "layers": args.layers, "batch": args.batch,
             "context": args.context, "new_tokens": int(out.shape[1] - ids.shape[1]),
             "prefill_s": t[1] - t[0], "decode_tokens_per_s": args.batch * steps / decode_s, "ms_per_decode_step": 1e3 * decode_s / steps,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30, "decode_stats": muzero.get_mu_zero_decode_stats()}

@@ -587,7 +587,7 @@ __device__ __forceinline__ long long record_of(const MzTilesPlan& tp, long long 
   return first_record + gw * tp.max_segs + (pair - (int)((unsigned)f0 / (unsigned)T));
 }
 template <bool WIDE>
-__global__ void __launch_bounds__(512) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
+__global__ void __launch_bounds__(512, 4) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
   __shared__ int s_slot[kMaxCombineSlots];     // record of candidate i, or -1
   __shared__ float s_part[WIDE ? 4 : 1][WIDE ? 130 : 1];
   const int pair = WIDE ? blockIdx.x / p.gqa : blockIdx.x;
