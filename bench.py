@@ -4,7 +4,7 @@
     python bench.py --impl reference-gpu      # context: the unmodified reference's own CUDA path on this GPU
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (BASELINE config 1 shape, one decode step of the hot path for a Qwen3-8B shaped
+Workload (one decode step of the hot path for a Qwen3-8B shaped
 model): per GPU 36 layers, each a quantized cache of batch 64 x 8 kv heads x (4096 packed +
 128 residual) tokens x head_dim 128, 32 query heads, 4-bit codes, group 64, fp16 metadata.
 A step is, for every layer: append the new K/V token, flush the residual window when due,
@@ -41,9 +41,9 @@ sys.path.insert(0, ROOT)
 
 LAYERS, BATCH, KVH, QH, CTX, RES, D, GROUP = 36, 64, 8, 32, 4096, 128, 128, 64
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mma_kernel launch at 4 bits, per sequence, from the
-# ncu capture summarised in profiles/decode_mma_4bit_b32.md (batch 32: 168.20 MB + 4.27 MB); traffic is
+# ncu capture summarised in profiles/decode_mma_4bit_b32.md (batch 32: 168.14 MB + 4.20 MB); traffic is
 # proportional to the batch, so a batch-64 launch is twice the captured one.
-NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_197_376 + 4_273_152) / 32
+NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_139_776 + 4_198_656) / 32
 METRIC = ("decode tokens/sec of the KV-cache hot path (append + flush + quantized decode attention, 36 layers, "
           "batch 64/GPU, ctx 4096+128)")
 
@@ -399,7 +399,7 @@ def run_attention_only(args) -> dict:
 
 def kv_split_point(bits: int, device, rank: int, world: int, dist, batch: int = 8, context: int = 131072, layers: int = 2,
                    steps: int = 6, warmup: int = 2, group: int = GROUP) -> dict:
-    """One point of the KV-sequence split (BASELINE config 4 shape): one very long context cut over the ranks' GPUs.
+    """One point of the KV-sequence split: one very long context cut over the ranks' GPUs.
     Each rank holds a contiguous slice of `context` quantized tokens (the last one also the residual window),
     computes its partial (m, l, acc); the triples are all-gathered (NCCL) and merged on every rank.  CUDA events
     around whole calls (partial + all-gather + merge), max over ranks."""
@@ -472,7 +472,7 @@ def run_kv_split(args) -> dict:
 
 
 def run_generate(args) -> dict:
-    """BASELINE config 2 (secondary workload): greedy `generate()` on a random-init (std 0.02)
+    """Secondary workload: greedy `generate()` on a random-init (std 0.02)
     Qwen3-8B-architecture decoder in bf16 through `patch_transformers()` and
     `cache_implementation="mu_zero_{bits}bit"`; decode-only tokens/s (prefill excluded, as the
     reference's throughput bench does).  `--cache dynamic` runs stock transformers for context;
@@ -514,6 +514,8 @@ def run_generate(args) -> dict:
             pass
 
     kwargs = dict(max_new_tokens=args.new_tokens, do_sample=False, pad_token_id=0)
+    if args.prefill_chunk:
+        kwargs["prefill_chunk_size"] = args.prefill_chunk      # long prompts: the model's own activations need it
     if args.cache == "mu_zero":
         kwargs.update(cache_implementation=f"mu_zero_{args.bits}bit",
                       cache_config={"q_group_size": GROUP, "residual_length": RES, "backend": "cuda"})
@@ -549,7 +551,7 @@ def run_generate(args) -> dict:
         cache_mb = {"cache_packed_mb": packed, "cache_meta_mb": meta, "cache_residual_mb": resid,
                     "cache_total_mb": packed + meta + resid}
     return {**cache_mb, "mode": "generate", "impl": args.impl, "cache": args.cache, "bits": args.bits, "layers": args.layers, "batch": args.batch,
-            "context": args.context, "new_tokens": int(out.shape[1] - ids.shape[1]),
+            "context": args.context, "prefill_chunk": args.prefill_chunk, "new_tokens": int(out.shape[1] - ids.shape[1]),
             "prefill_s": t[1] - t[0], "decode_tokens_per_s": args.batch * steps / decode_s, "ms_per_decode_step": 1e3 * decode_s / steps,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30, "decode_stats": muzero.get_mu_zero_decode_stats()}
 
@@ -700,6 +702,7 @@ def main():
     ap.add_argument("--context", type=int, default=CTX, help="quantized tokens per sequence (--attention-only, --generate)")
     ap.add_argument("--group", type=int, default=GROUP, help="quantization group size (--attention-only)")
     ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="--generate: prefill the prompt in chunks of this many tokens")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.generate:

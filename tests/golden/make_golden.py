@@ -13,7 +13,7 @@ Outputs (all small, committed):
   layer_cases.npz     MuZeroCacheLayer states (prefill flush, per-token decode
                       flush) and decode-attention outputs (as-is and fp32 evaluation)
   layer_cases_logq.npz  the same for ``logq_compatible_layout=True`` (``--only logq`` writes just these)
-  config0.npz         BASELINE config 0 at full size: sha256 of every store
+  config0.npz         batch 1 x 8 kv heads x 4096 tokens x head_dim 128 (4-bit, group 64, residual 128) at full size: sha256 of every store
                       tensor + the attention outputs
   alpha_cases.json    ``select_alpha`` results on the synthetic distributions
 
