@@ -516,6 +516,8 @@ def run_generate(args) -> dict:
     kwargs = dict(max_new_tokens=args.new_tokens, do_sample=False, pad_token_id=0)
     if args.prefill_chunk:
         kwargs["prefill_chunk_size"] = args.prefill_chunk      # long prompts: the model's own activations need it
+        # ... and the cache quantizes chunk by chunk, as the reference's bench does in its chunked mode
+        os.environ["MUZERO_QUANTIZE_PREFILL_CHUNKS"] = "1"
     if args.cache == "mu_zero":
         kwargs.update(cache_implementation=f"mu_zero_{args.bits}bit",
                       cache_config={"q_group_size": GROUP, "residual_length": RES, "backend": "cuda"})

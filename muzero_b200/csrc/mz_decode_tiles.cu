@@ -685,6 +685,70 @@ __global__ void __launch_bounds__(512, 4) combine_tiles_kernel(const MzDecodePar
   }
 }
 
+// The common case (one plan, a handful of records per pair): one WARP per (pair, head), no shared memory and no
+// block barrier.  Each lane finds one candidate's record before the wait (pure arithmetic), then up to eight
+// records are loaded at once (their m / l words and one float4 of acc per lane) and merged in candidate order.
+__global__ void __launch_bounds__(256) combine_tiles_warp_kernel(const MzDecodeParams p, const MzDecodeOut o) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long rows = (long long)p.s.batch * p.H;
+  const int gqa = p.gqa;
+  const int pair = (int)(row / gqa), h = (int)(row % gqa);
+  const bool live = row < rows;
+  const WorkerRange cr = live ? candidate_workers(p.tp, pair) : WorkerRange{0, -1};
+  // candidates in chunks of 32 (one per lane); nearly always one chunk
+  long long my_rec = -1;
+  if (cr.first + lane <= cr.last) my_rec = record_of(p.tp, cr.first + lane, pair, 0);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!live) return;
+  float mx = -INFINITY, lsum = 0.f;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long base = cr.first; base <= cr.last; base += 32) {
+    if (base != cr.first) my_rec = base + lane <= cr.last ? record_of(p.tp, base + lane, pair, 0) : -1;
+    unsigned todo = __ballot_sync(0xffffffffu, my_rec >= 0);
+    while (todo) {
+      float mi[8], li[8];
+      float4 ai[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool on = todo != 0;
+        const int src = on ? __ffs(todo) - 1 : 0;
+        if (on) todo &= todo - 1;
+        const long long rec = __shfl_sync(0xffffffffu, my_rec, src);
+        const long long slot = on ? rec * gqa + h : 0;
+        mi[j] = on ? p.part.m[slot] : -INFINITY;
+        li[j] = on ? p.part.l[slot] : 0.f;
+        ai[j] = on ? *((const float4*)(p.part.acc + slot * D) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float m_new = mx;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m_new = fmaxf(m_new, mi[j]);
+      const float keep = mx > -INFINITY ? __expf(mx - m_new) : 0.f;
+      lsum *= keep; a.x *= keep; a.y *= keep; a.z *= keep; a.w *= keep;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float wgt = mi[j] > -INFINITY ? __expf(mi[j] - m_new) : 0.f;
+        lsum = fmaf(li[j], wgt, lsum);
+        a.x = fmaf(ai[j].x, wgt, a.x); a.y = fmaf(ai[j].y, wgt, a.y);
+        a.z = fmaf(ai[j].z, wgt, a.z); a.w = fmaf(ai[j].w, wgt, a.w);
+      }
+      mx = m_new;
+    }
+  }
+  const int d = 4 * lane;
+  if (o.out) {
+    const float den = fmaxf(lsum, 1e-20f);
+    mz_store_from_float(o.out, row * D + d, a.x / den, o.out_dt);
+    mz_store_from_float(o.out, row * D + d + 1, a.y / den, o.out_dt);
+    mz_store_from_float(o.out, row * D + d + 2, a.z / den, o.out_dt);
+    mz_store_from_float(o.out, row * D + d + 3, a.w / den, o.out_dt);
+  } else {
+    float* dst = o.acc + row * o.acc_stride + d;
+    dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+    if (lane == 0) { o.m[row * o.ml_stride] = mx; o.l[row * o.ml_stride] = lsum; }
+  }
+}
+
 template <int BITS, int G, int GQA>
 int launch_one(const MzDecodeParams& p, cudaStream_t st) {
   auto kern = decode_tiles_kernel<BITS, G, GQA>;
@@ -852,7 +916,14 @@ int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (wide) MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_kernel<true>, p, o));
+  // one plan and a few records per pair (workers per pair below 8): the warp-per-row kernel
+  const bool per_warp = !wide && p.tp2.total_warps == 0 && p.tp.total_warps / pairs < 8;
+  if (per_warp) {
+    cfg.blockDim = dim3(256);
+    cfg.gridDim = dim3((unsigned)((pairs * p.gqa + 7) / 8));
+  }
+  if (per_warp) MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_warp_kernel, p, o));
+  else if (wide) MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_kernel<true>, p, o));
   else MZ_CUDA(cudaLaunchKernelEx(&cfg, mzt::combine_tiles_kernel<false>, p, o));
   MZ_LAUNCH_CHECK("combine_tiles");
   return MZ_OK;

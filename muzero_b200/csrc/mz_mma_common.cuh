@@ -86,7 +86,11 @@ __device__ __forceinline__ __half2 dup_hi(uint32_t v) { return __half2half2(__hi
 template <int BITS>
 __device__ __forceinline__ void fill_lookup_table(float alpha_key, float alpha_value) {
   constexpr int NE = 1 << BITS, TOP = NE - 1;
-  for (int i = threadIdx.x; i < 2 * NE * NE; i += blockDim.x) {
+  // one table when keys and values use the same alpha (the usual case): each entry is computed once and stored
+  // to both halves of its 256-byte slot
+  const bool same = alpha_key == alpha_value;
+  const int n = same ? NE * NE : 2 * NE * NE;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int which = i / (NE * NE), idx = i % (NE * NE);
     const int zc = idx >> BITS, e = idx & TOP;
     const float alpha = which ? alpha_value : alpha_key;
@@ -109,6 +113,10 @@ __device__ __forceinline__ void fill_lookup_table(float alpha_key, float alpha_v
     const uint32_t row = TBL + idx * 256 + which * 128;
 #pragma unroll 4
     for (int c = 0; c < 32; ++c) sts32(row + (((c + threadIdx.x) & 31) << 2), bits);
+    if (same) {
+#pragma unroll 4
+      for (int c = 0; c < 32; ++c) sts32(row + 128 + (((c + threadIdx.x) & 31) << 2), bits);
+    }
   }
 }
 

@@ -50,6 +50,11 @@ class MuZeroCache(_HFCache):
         self.parity_mode = os.environ.get("MUZERO_PARITY_MODE", "0") == "1"
         self.fused_step = (self.fused_decode and not self.parity_mode
                            and os.environ.get("MUZERO_DISABLE_DECODE_STEP", "0") != "1")
+        # MUZERO_QUANTIZE_PREFILL_CHUNKS=1 -> a chunked prefill quantizes every chunk as it arrives, as the
+        # reference's throughput bench does when it prefills in chunks (benchmarks/bench_throughput.py:244-279:
+        # no deferral there), instead of keeping every layer's dense K/V until the first decode step, as its
+        # generate() hook does.  Later chunks then attend to dequantized earlier tokens; memory stays bounded.
+        self.quantize_prefill_chunks = os.environ.get("MUZERO_QUANTIZE_PREFILL_CHUNKS", "0") == "1"
         if _HFCache is object:
             self.layers = []
             self.layer_class_to_replicate = None
@@ -90,6 +95,8 @@ class MuZeroCache(_HFCache):
         block, so tokens do not change; what changes is that only the residual window stays dense.  A chunked
         prefill keeps the reference's deferral: later chunks attend to the exact dense K/V of earlier ones."""
         if not self.defer_prefill_quantization:
+            return False
+        if self.quantize_prefill_chunks and not self.single_shot_prefill:
             return False
         first_block = layer_idx >= len(self.layers) or not self.layers[layer_idx].is_initialized
         return not (self.single_shot_prefill and first_block)
