@@ -329,11 +329,15 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
   cur.pair = (int)((unsigned)f0 / (unsigned)T); cur.tile = (int)((unsigned)f0 % (unsigned)T);
   cur.b = cur.pair / s.kv_heads; cur.kvh = cur.pair % s.kv_heads;
   Cursor nxt = cur;
-  // the first tile's copies are in flight while the CTA builds its lookup table
-  stage_k(cur, active);
-  stage_v(cur, active);
+  // Everything up to here reads kernel parameters only, and the table build touches shared memory only: when the
+  // kernel was launched as a programmatic dependent of the previous kernel in the stream (the merge kernel of the
+  // previous call, the append of this step) this prologue runs while that kernel drains.  Global memory is first
+  // touched after the wait.
   if (kt > 0) fill_lookup_table<BITS>(s.alpha_key, s.alpha_value);
   for (int i = lane; i < PBUF_BYTES / 4; i += 32) sts32(L.pbuf + i * 4, 0u);   // the odd columns stay zero for good
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  stage_k(cur, active);
+  stage_v(cur, active);
   __syncthreads();
   if (!active) return;
   reset_state();
@@ -609,7 +613,19 @@ template <int BITS, int GQA>
 int launch_one(const MzDecodeParams& p, cudaStream_t st) {
   auto kern = decode_mma_kernel<BITS, GQA>;
   MZ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.tp.smem_bytes));
-  kern<<<(unsigned)p.tp.ctas, p.tp.warps_per_cta * 32, p.tp.smem_bytes, st>>>(p);
+  // programmatic dependent launch: harmless after a kernel that never signals (the launch then happens at its
+  // completion, as usual); after one that does, the prologue overlaps it
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)p.tp.ctas);
+  cfg.blockDim = dim3((unsigned)p.tp.warps_per_cta * 32);
+  cfg.dynamicSmemBytes = p.tp.smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MZ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
   MZ_LAUNCH_CHECK("decode_mma");
   return MZ_OK;
 }

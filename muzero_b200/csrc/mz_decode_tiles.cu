@@ -588,6 +588,7 @@ __device__ __forceinline__ long long record_of(const MzTilesPlan& tp, long long 
 }
 template <bool WIDE>
 __global__ void __launch_bounds__(512, 4) combine_tiles_kernel(const MzDecodeParams p, const MzDecodeOut o) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent waits for this grid's completion itself
   __shared__ int s_slot[kMaxCombineSlots];     // record of candidate i, or -1
   __shared__ float s_part[WIDE ? 4 : 1][WIDE ? 130 : 1];
   const int pair = WIDE ? blockIdx.x / p.gqa : blockIdx.x;
@@ -689,6 +690,7 @@ __global__ void __launch_bounds__(512, 4) combine_tiles_kernel(const MzDecodePar
 // block barrier.  Each lane finds one candidate's record before the wait (pure arithmetic), then up to eight
 // records are loaded at once (their m / l words and one float4 of acc per lane) and merged in candidate order.
 __global__ void __launch_bounds__(256) combine_tiles_warp_kernel(const MzDecodeParams p, const MzDecodeOut o) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent waits for this grid's completion itself
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long rows = (long long)p.s.batch * p.H;

@@ -210,6 +210,10 @@ __global__ void __launch_bounds__(256) flush_kv_kernel(const FlushParams p) {
 
 __global__ void append_kv_kernel(const mz_kv_store s, const uint16_t* __restrict__ k_new, const uint16_t* __restrict__ v_new,
                                  long long nsb, long long nsh) {
+  // launched as a programmatic dependent: nothing is read or written before the previous kernel has completed,
+  // and the next kernel (the decode attention) may start its own prologue right away
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int D = s.head_dim;
   const long long n = (long long)s.batch * s.kv_heads * D;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -327,7 +331,16 @@ extern "C" int mz_append_kv(const mz_kv_store* s, const void* k_new, const void*
   if ((rc = mz_check_store_residual(s))) return rc;
   MZ_REQUIRE(k_new && v_new, "NULL new token pointer");
   const long long n = (long long)s->batch * s->kv_heads * s->head_dim;
-  append_kv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*s, (const uint16_t*)k_new, (const uint16_t*)v_new, nsb, nsh);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((n + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MZ_CUDA(cudaLaunchKernelEx(&cfg, append_kv_kernel, *s, (const uint16_t*)k_new, (const uint16_t*)v_new, nsb, nsh));
   MZ_LAUNCH_CHECK("append_kv");
   return MZ_OK;
 }
