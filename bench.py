@@ -17,7 +17,8 @@ scales, q~N(0,1), seeded.
             with pinned host q/k/v copied in and the attention output copied out every step
             (copies on a second stream, overlapped with the layers' kernels)
   roofline  algorithmic bytes of one decode-attention call / its mean duration (CUDA events on
-            the launch stream, timed region only) against the measured HBM copy bandwidth
+            the launch stream around one call per step of the timed region, a different layer each
+            step) against the measured HBM copy bandwidth
   cpu_baseline / --impl reference
             the CPU restatement of the reference's PyTorch path (oracle/) on the host cores,
             on a bounded sample of the same workload
@@ -199,18 +200,23 @@ class CabiSession:
         self.launches = 0
         self.attn_events = []
 
-    def step(self, time_attention: bool):
+    def step(self, timed_layer: int = -1):
+        """One decode step.  `timed_layer`: the layer whose attention call is bracketed by CUDA events in this step
+        (-1: none).  Only one call per step is bracketed: an event record between two kernels keeps the second
+        from starting its prologue while the first drains (programmatic dependent launch), so events around every
+        call would slow the step they measure."""
         lib, st = self.lib, self.stream
         for i, layer in enumerate(self.layers):
             before = layer._key_group_count
             layer.update(self.k_new, self.v_new, {"materialize_full_kv": False})   # append (+ flush when due)
             self.launches += 1 + (1 if layer._key_group_count != before else 0)
             args = self.build(layer, self.q, D ** -0.5, None, self.outs[i])
-            if time_attention:
+            timed = i == timed_layer
+            if timed:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             rc = lib.mz_decode_attention(ctypes.byref(args), st)
-            if time_attention:
+            if timed:
                 e1.record()
                 self.attn_events.append((e0, e1))
             if rc != 0:
@@ -254,7 +260,7 @@ def run_ours(args) -> dict:
     # ---------------- device-resident throughput through the C ABI
     sess = CabiSession(layers, q, k_new, v_new)
     for _ in range(args.warmup):
-        sess.step(False)
+        sess.step()
     barrier()
     sess.launches = 0
     sampler = ClockSampler(local)
@@ -262,8 +268,8 @@ def run_ours(args) -> dict:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        sess.step(True)
+    for i in range(args.steps):
+        sess.step(timed_layer=(7 * i) % L)     # one bracketed attention call per step, a different layer each time
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -334,6 +340,8 @@ def run_ours(args) -> dict:
         torch.cuda.empty_cache()
         other = 2 if bits == 4 else 4
         extra[f"roofline_{other}bit"] = time_attention(other, device, B, CTX, layers=4)
+        # the benched width again, calls back to back without events in between (what the step itself sees)
+        extra[f"roofline_{bits}bit_back_to_back"] = time_attention(bits, device, B, CTX, layers=4)
         extra["ctx_sweep"] = [time_attention(bits, device, B, c, layers=2, steps=6) for c in (8192, 32768)]
         barrier()
         if world > 1:

@@ -107,6 +107,7 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   p.eps = 1e-8f;
   p.v_lead = v_lead;
   p.table_k = p.table_v = nullptr;
+  p.lut = nullptr;
   const int force = kernel_override();
   plan->tiles = force != 1 && mz_decode_tiles_supported(p);
   if (v_lead > 0 && !plan->tiles)

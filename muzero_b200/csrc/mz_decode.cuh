@@ -74,6 +74,9 @@ struct MzDecodeParams {
   // total_warps == 0 when there is no residual window); the records of tp2 start at record slots_a
   MzTilesPlan tp2;
   long long slots_a;
+  // tensor-core kernel: the lookup-table entries in global memory (built once per device and (bits, alphas));
+  // nullptr = every CTA computes them itself
+  const unsigned* lut;
 };
 
 // where a call's result goes: normalised output, or the merged (m, l, acc) triple.  The triple is addressed

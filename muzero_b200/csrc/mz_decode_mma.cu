@@ -333,7 +333,10 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
   // kernel was launched as a programmatic dependent of the previous kernel in the stream (the merge kernel of the
   // previous call, the append of this step) this prologue runs while that kernel drains.  Global memory is first
   // touched after the wait.
-  if (kt > 0) fill_lookup_table<BITS>(s.alpha_key, s.alpha_value);
+  if (kt > 0) {
+    if (p.lut != nullptr) fill_lookup_table_from<BITS>(p.lut);      // written long before the previous kernel started
+    else fill_lookup_table<BITS>(s.alpha_key, s.alpha_value);
+  }
   for (int i = lane; i < PBUF_BYTES / 4; i += 32) sts32(L.pbuf + i * 4, 0u);   // the odd columns stay zero for good
   asm volatile("griddepcontrol.wait;" ::: "memory");
   stage_k(cur, active);
@@ -642,7 +645,55 @@ int launch_gqa(const MzDecodeParams& p, cudaStream_t st) {
 constexpr int kMaxDevices = 64;
 std::mutex g_mu;
 int g_window_base[kMaxDevices];      // 0 = not probed yet, -1 = probe failed, else the address
+
+// Lookup-table entries kept in a static device array (no allocation): one slot per (bits, alpha of keys, alpha
+// of values) seen on a device.
+constexpr int kLutSlots = 16;
+__device__ uint32_t g_lut[kLutSlots][512];
+template <int BITS>
+__global__ void build_lut_kernel(int slot, float alpha_key, float alpha_value) {
+  constexpr int NE = 1 << BITS;
+  for (int i = threadIdx.x; i < 2 * NE * NE; i += blockDim.x)
+    g_lut[slot][i] = lookup_entry<BITS>(i / (NE * NE) ? alpha_value : alpha_key, i % (NE * NE));
+}
+struct LutKey { int bits; float ak, av; };
+struct LutDevice { uint32_t* base; int used; LutKey keys[kLutSlots]; };
+LutDevice g_lut_dev[kMaxDevices];
 }  // namespace mzm
+
+// Device pointer to the table entries for (bits, alphas) on the current device, or nullptr when they cannot be
+// provided (all slots taken, or the one-time build is not possible right now, e.g. during stream capture): the
+// kernel then computes the entries in every CTA.  The first request for a combination launches a one-block
+// kernel on the default stream and waits for it, so that any stream may use the entries afterwards.
+const unsigned* mz_mma_lookup_entries(int bits, float alpha_key, float alpha_value) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= mzm::kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lk(mzm::g_mu);
+  mzm::LutDevice& d = mzm::g_lut_dev[dev];
+  for (int i = 0; i < d.used; ++i)
+    if (d.keys[i].bits == bits && d.keys[i].ak == alpha_key && d.keys[i].av == alpha_value) return d.base + i * 512;
+  if (d.used >= mzm::kLutSlots) return nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(cudaStreamLegacy, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  if (d.base == nullptr && cudaGetSymbolAddress((void**)&d.base, mzm::g_lut) != cudaSuccess) {
+    (void)cudaGetLastError();
+    d.base = nullptr;
+    return nullptr;
+  }
+  const int slot = d.used;
+  if (bits == 4) mzm::build_lut_kernel<4><<<1, 256>>>(slot, alpha_key, alpha_value);
+  else mzm::build_lut_kernel<2><<<1, 32>>>(slot, alpha_key, alpha_value);
+  if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(cudaStreamLegacy) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  d.keys[slot] = {bits, alpha_key, alpha_value};
+  d.used = slot + 1;
+  return d.base + slot * 512;
+}
 
 // Shared-window address at which this device places dynamic shared memory (a kernel without static shared
 // memory).  The tensor-core kernel addresses its buffers absolutely (the lookup table must sit at 65536),
@@ -697,6 +748,7 @@ int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slo
   if ((unsigned)warps > (window_end - high_base) / per_high) warps = (int)((window_end - high_base) / per_high);
   if (warps < 1) return mz_fail(MZ_ERR_UNSUPPORTED, "tile does not fit shared memory");
   t.kind = 1;
+  p.lut = s.k_groups > 0 ? mz_mma_lookup_entries(s.bits, s.alpha_key, s.alpha_value) : nullptr;
   t.stage_bytes = sb;
   t.low_base = low_base;
   t.high_base = high_base;

@@ -83,40 +83,56 @@ __device__ __forceinline__ __half2 dup_hi(uint32_t v) { return __half2half2(__hi
 // of an entry carries the fp16 remainder of the active half, pre-scaled by the nominal ratio Bdn / Bup of a row
 // in that zero-code bin (anchor at the bin centre); the end bins have codes on one side only and row_constants
 // makes their two constants equal.  Called by every thread of the CTA; the caller synchronises afterwards.
+// entry idx = (zc << BITS | e) of the table for `alpha`, as the bits of half2(u+, u-)
+template <int BITS>
+__device__ __forceinline__ uint32_t lookup_entry(float alpha, int idx) {
+  constexpr int NE = 1 << BITS, TOP = NE - 1;
+  const int zc = idx >> BITS, e = idx & TOP;
+  const float lb = log1pf(alpha);
+  const float zac = (float)zc / (float)TOP;
+  const float ratio = (zc == 0 || zc == TOP) ? 1.0f : zac / (1.0f - zac);
+  __half2 ent;
+  if (e >= zc) {
+    const int up = max(TOP - zc, 1);
+    const float u = expm1f((float)min(e - zc, up) / (float)up * lb) / alpha;
+    const float uh = __half2float(__float2half_rn(u));
+    ent = __floats2half2_rn(uh, (u - uh) / ratio);
+  } else {
+    const int dn = max(zc, 1);
+    const float u = -expm1f((float)(zc - e) / (float)dn * lb) / alpha;
+    const float uh = __half2float(__float2half_rn(u));
+    ent = __floats2half2_rn((u - uh) * ratio, uh);
+  }
+  return h2_bits(ent);
+}
+// stores one entry to the 32 lane copies of its slot half (rotated so that the lanes of a warp, which hold
+// consecutive entries, hit different banks)
+__device__ __forceinline__ void store_entry_copies(uint32_t row, uint32_t bits) {
+#pragma unroll 4
+  for (int c = 0; c < 32; ++c) sts32(row + (((c + threadIdx.x) & 31) << 2), bits);
+}
 template <int BITS>
 __device__ __forceinline__ void fill_lookup_table(float alpha_key, float alpha_value) {
-  constexpr int NE = 1 << BITS, TOP = NE - 1;
+  constexpr int NE = 1 << BITS;
   // one table when keys and values use the same alpha (the usual case): each entry is computed once and stored
   // to both halves of its 256-byte slot
   const bool same = alpha_key == alpha_value;
   const int n = same ? NE * NE : 2 * NE * NE;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int which = i / (NE * NE), idx = i % (NE * NE);
-    const int zc = idx >> BITS, e = idx & TOP;
-    const float alpha = which ? alpha_value : alpha_key;
-    const float lb = log1pf(alpha);
-    const float zac = (float)zc / (float)TOP;
-    const float ratio = (zc == 0 || zc == TOP) ? 1.0f : zac / (1.0f - zac);
-    __half2 ent;
-    if (e >= zc) {
-      const int up = max(TOP - zc, 1);
-      const float u = expm1f((float)min(e - zc, up) / (float)up * lb) / alpha;
-      const float uh = __half2float(__float2half_rn(u));
-      ent = __floats2half2_rn(uh, (u - uh) / ratio);
-    } else {
-      const int dn = max(zc, 1);
-      const float u = -expm1f((float)(zc - e) / (float)dn * lb) / alpha;
-      const float uh = __half2float(__float2half_rn(u));
-      ent = __floats2half2_rn((u - uh) * ratio, uh);
-    }
-    const uint32_t bits = h2_bits(ent);
-    const uint32_t row = TBL + idx * 256 + which * 128;
-#pragma unroll 4
-    for (int c = 0; c < 32; ++c) sts32(row + (((c + threadIdx.x) & 31) << 2), bits);
-    if (same) {
-#pragma unroll 4
-      for (int c = 0; c < 32; ++c) sts32(row + 128 + (((c + threadIdx.x) & 31) << 2), bits);
-    }
+    const uint32_t bits = lookup_entry<BITS>(which ? alpha_value : alpha_key, idx);
+    store_entry_copies(TBL + idx * 256 + which * 128, bits);
+    if (same) store_entry_copies(TBL + idx * 256 + 128, bits);
+  }
+}
+// the same table from a copy in global memory: [2][NE * NE] entries (keys' alpha, values' alpha), built once
+// per device and (bits, alphas) by the host side
+template <int BITS>
+__device__ __forceinline__ void fill_lookup_table_from(const uint32_t* __restrict__ entries) {
+  constexpr int NE = 1 << BITS;
+  for (int i = threadIdx.x; i < 2 * NE * NE; i += blockDim.x) {
+    const int which = i / (NE * NE), idx = i % (NE * NE);
+    store_entry_copies(TBL + idx * 256 + which * 128, entries[i]);
   }
 }
 
