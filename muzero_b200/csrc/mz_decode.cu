@@ -108,6 +108,7 @@ int make_plan(const mz_decode_args* a, Plan* plan, bool need_tables) {
   p.v_lead = v_lead;
   p.table_k = p.table_v = nullptr;
   p.lut = nullptr;
+  p.hetero = 0;
   const int force = kernel_override();
   plan->tiles = force != 1 && mz_decode_tiles_supported(p);
   if (v_lead > 0 && !plan->tiles)

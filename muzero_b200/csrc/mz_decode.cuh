@@ -77,6 +77,9 @@ struct MzDecodeParams {
   // tensor-core kernel: the lookup-table entries in global memory (built once per device and (bits, alphas));
   // nullptr = every CTA computes them itself
   const unsigned* lut;
+  // tensor-core kernel, one launch over two plans: CTAs [0, hetero) work on plan `tp` (packed tiles only), the
+  // rest on plan `tp2` (residual tiles only, records from slots_a on).  0 = one plan per launch.
+  int hetero;
 };
 
 // where a call's result goes: normalised output, or the merged (m, l, acc) triple.  The triple is addressed

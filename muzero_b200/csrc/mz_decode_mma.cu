@@ -137,21 +137,26 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
 
   // tiles 0 .. kt-1 of a pair are packed groups, the rest residual tiles; a plan without packed tiles (the
   // residual-only companion launch of the tcgen05 kernel) needs no table
-  const int kt = p.tp.packed_tiles;
+  // one launch may carry two plans: the first p.hetero CTAs take the packed tiles, the others the residual tiles
+  // (a residual tile is a short latency-bound chain; kept apart it no longer sits in the packed tiles' warps)
+  const bool second = p.hetero > 0 && (int)blockIdx.x >= p.hetero;
+  const MzTilesPlan& tp = second ? p.tp2 : p.tp;
+  const long long first_record = second ? p.slots_a : 0;      // in records of one head
+  const int kt = tp.packed_tiles;
 
-  const int W = p.tp.total_warps, T = p.tp.tiles_per_pair;
-  const int gw = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int W = tp.total_warps, T = tp.tiles_per_pair;
+  const int gw = ((int)blockIdx.x - (second ? p.hetero : 0)) * (blockDim.x >> 5) + warp;
   long long f0 = 0, f1 = 0;
-  if (gw < W) mz_warp_tiles(p.tp, gw, &f0, &f1);
+  if (gw < W) mz_warp_tiles(tp, gw, &f0, &f1);
 
   // ---- this warp's buffers (absolute shared-window addresses; the planner sized the pools)
   const int msz = s.meta_dtype == MZ_F32 ? 4 : 2;
-  const uint32_t SB = p.tp.stage_bytes;
+  const uint32_t SB = tp.stage_bytes;
   const uint32_t nw = blockDim.x >> 5;
   Layout L;
-  L.kbuf = p.tp.low_base + warp * SB;
-  L.aK = p.tp.low_base + nw * SB + warp * A_BYTES;
-  const uint32_t hb = p.tp.high_base + warp * (SB + 2 * RI_BYTES + A_BYTES + PBUF_BYTES);
+  L.kbuf = tp.low_base + warp * SB;
+  L.aK = tp.low_base + nw * SB + warp * A_BYTES;
+  const uint32_t hb = tp.high_base + warp * (SB + 2 * RI_BYTES + A_BYTES + PBUF_BYTES);
   L.vbuf = hb;
   L.riK = hb + SB;
   L.riV = L.riK + RI_BYTES;
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) decode_mma_kernel(const MzD
       b1 += __shfl_xor_sync(0xffffffffu, b1, off);
     }
     if (t < GQA) {
-      const long long slot = ((long long)gw * p.tp.max_segs + seg) * GQA + t;
+      const long long slot = first_record + ((long long)gw * tp.max_segs + seg) * GQA + t;
       if (!MZ_IN_BOUNDS(slot, p.part.slots, 10)) return;
       float* dst = p.part.acc + slot * D + 8 * g;
       float4 v;
@@ -619,7 +624,7 @@ int launch_one(const MzDecodeParams& p, cudaStream_t st) {
   // programmatic dependent launch: harmless after a kernel that never signals (the launch then happens at its
   // completion, as usual); after one that does, the prologue overlaps it
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)p.tp.ctas);
+  cfg.gridDim = dim3((unsigned)(p.hetero > 0 ? p.tp.ctas + p.tp2.ctas : p.tp.ctas));
   cfg.blockDim = dim3((unsigned)p.tp.warps_per_cta * 32);
   cfg.dynamicSmemBytes = p.tp.smem_bytes;
   cfg.stream = st;
@@ -728,7 +733,50 @@ bool mz_decode_mma_supported(const MzDecodeParams& p) {
   return mz_smem_window_base() > 0;
 }
 
+namespace {
+int plan_single(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots);
+}
+// Cost of a residual tile in CTAs that hold residual tiles only, in the units of cost_q = 64 for a packed tile
+// among 12 busy warps (6.4 us).  Such a warp is bound by memory latency (its copies run one tile ahead and a
+// tile's arithmetic is short): 2.4 us per tile, measured by sweeping this constant (8 .. 48) at residual lengths
+// 128 and 192.
+constexpr int kDenseCtaCost = 24;
+
 int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots) {
+  const mz_kv_store& s = p.s;
+  p.hetero = 0;
+  const long long pairs = (long long)s.batch * s.kv_heads;
+  const int dense_tiles = (s.res_len + mzm::DT - 1) / mzm::DT;
+  // enough packed work to fill every warp of the machine, and a residual window: split the CTAs
+  if (splits_request == 0 && s.k_groups > 0 && dense_tiles > 0 && sm_count >= 8 &&
+      pairs * s.k_groups >= (long long)sm_count * mzm::MAX_WARPS * 2) {
+    const long long cost_d = (long long)dense_tiles * kDenseCtaCost, cost_p = (long long)s.k_groups * 64;
+    int n_d = (int)((sm_count * cost_d + cost_d + cost_p - 1) / (cost_d + cost_p));
+    if (n_d < 1) n_d = 1;
+    if (n_d > sm_count / 2) n_d = sm_count / 2;
+    MzDecodeParams a = p, b = p;
+    a.s.res_len = 0;
+    b.s.k_groups = 0; b.s.v_tokens = 0;
+    size_t slots_a = 0, slots_b = 0;
+    int rc = plan_single(a, 0, sm_count - n_d, &slots_a);
+    if (rc == MZ_OK) rc = plan_single(b, 0, n_d, &slots_b);
+    const bool same_shape = rc == MZ_OK && a.tp.warps_per_cta == b.tp.warps_per_cta && a.tp.smem_bytes == b.tp.smem_bytes &&
+                            a.tp.stage_bytes == b.tp.stage_bytes && a.tp.low_base == b.tp.low_base && a.tp.high_base == b.tp.high_base;
+    if (same_shape) {
+      p.tp = a.tp;
+      p.tp2 = b.tp;
+      p.lut = a.lut;
+      p.slots_a = (long long)slots_a;
+      p.hetero = a.tp.ctas;
+      *slots = slots_a + slots_b;
+      return MZ_OK;
+    }
+  }
+  return plan_single(p, splits_request, sm_count, slots);
+}
+
+namespace {
+int plan_single(MzDecodeParams& p, int splits_request, int sm_count, size_t* slots) {
   const mz_kv_store& s = p.s;
   MzTilesPlan& t = p.tp;
   const int msz = s.meta_dtype == MZ_F32 ? 4 : 2;
@@ -789,6 +837,8 @@ int mz_plan_mma(MzDecodeParams& p, int splits_request, int sm_count, size_t* slo
   *slots = (size_t)W * t.max_segs * p.gqa;
   return MZ_OK;
 }
+
+}  // namespace
 
 int mz_launch_decode_mma(const MzDecodeParams& p, cudaStream_t st) {
   if (p.s.bits == 4) return mzm::launch_gqa<4>(p, st);

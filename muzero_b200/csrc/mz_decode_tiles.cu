@@ -686,9 +686,10 @@ __global__ void __launch_bounds__(512, 4) combine_tiles_kernel(const MzDecodePar
   }
 }
 
-// The common case (one plan, a handful of records per pair): one WARP per (pair, head), no shared memory and no
-// block barrier.  Each lane finds one candidate's record before the wait (pure arithmetic), then up to eight
-// records are loaded at once (their m / l words and one float4 of acc per lane) and merged in candidate order.
+// The common case (a handful of records per pair): one WARP per (pair, head), no shared memory and no block
+// barrier.  Each lane finds one candidate's record before the wait (pure arithmetic), then up to eight records
+// are loaded at once (their m / l words and one float4 of acc per lane) and merged in candidate order; the
+// records of a second plan (residual tiles of a split launch) follow those of the first.
 __global__ void __launch_bounds__(256) combine_tiles_warp_kernel(const MzDecodeParams p, const MzDecodeOut o) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent waits for this grid's completion itself
   const int lane = threadIdx.x & 31;
@@ -697,16 +698,18 @@ __global__ void __launch_bounds__(256) combine_tiles_warp_kernel(const MzDecodeP
   const int gqa = p.gqa;
   const int pair = (int)(row / gqa), h = (int)(row % gqa);
   const bool live = row < rows;
-  const WorkerRange cr = live ? candidate_workers(p.tp, pair) : WorkerRange{0, -1};
-  // candidates in chunks of 32 (one per lane); nearly always one chunk
-  long long my_rec = -1;
-  if (cr.first + lane <= cr.last) my_rec = record_of(p.tp, cr.first + lane, pair, 0);
+  const WorkerRange ca = live ? candidate_workers(p.tp, pair) : WorkerRange{0, -1};
+  const WorkerRange cb = live ? candidate_workers(p.tp2, pair) : WorkerRange{0, -1};
+  const long long first_b = p.slots_a / gqa;
+  // first chunk of candidates of each plan (one per lane); nearly always the only chunk
+  long long rec_a = -1, rec_b = -1;
+  if (ca.first + lane <= ca.last) rec_a = record_of(p.tp, ca.first + lane, pair, 0);
+  if (cb.first + lane <= cb.last) rec_b = record_of(p.tp2, cb.first + lane, pair, first_b);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (!live) return;
   float mx = -INFINITY, lsum = 0.f;
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (long long base = cr.first; base <= cr.last; base += 32) {
-    if (base != cr.first) my_rec = base + lane <= cr.last ? record_of(p.tp, base + lane, pair, 0) : -1;
+  auto merge_chunk = [&](long long my_rec) {
     unsigned todo = __ballot_sync(0xffffffffu, my_rec >= 0);
     while (todo) {
       float mi[8], li[8];
@@ -736,6 +739,14 @@ __global__ void __launch_bounds__(256) combine_tiles_warp_kernel(const MzDecodeP
       }
       mx = m_new;
     }
+  };
+  for (long long base = ca.first; base <= ca.last; base += 32) {
+    if (base != ca.first) rec_a = base + lane <= ca.last ? record_of(p.tp, base + lane, pair, 0) : -1;
+    merge_chunk(rec_a);
+  }
+  for (long long base = cb.first; base <= cb.last; base += 32) {
+    if (base != cb.first) rec_b = base + lane <= cb.last ? record_of(p.tp2, base + lane, pair, first_b) : -1;
+    merge_chunk(rec_b);
   }
   const int d = 4 * lane;
   if (o.out) {
@@ -919,7 +930,7 @@ int mz_combine_tiles(const MzDecodeParams& p, const MzDecodeOut& o, cudaStream_t
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   // one plan and a few records per pair (workers per pair below 8): the warp-per-row kernel
-  const bool per_warp = !wide && p.tp2.total_warps == 0 && p.tp.total_warps / pairs < 8;
+  const bool per_warp = !wide && (p.tp2.total_warps == 0 || p.hetero > 0) && p.tp.total_warps / pairs < 8;
   if (per_warp) {
     cfg.blockDim = dim3(256);
     cfg.gridDim = dim3((unsigned)((pairs * p.gqa + 7) / 8));
