@@ -42,9 +42,9 @@ sys.path.insert(0, ROOT)
 
 LAYERS, BATCH, KVH, QH, CTX, RES, D, GROUP = 36, 64, 8, 32, 4096, 128, 128, 64
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mma_kernel launch at 4 bits, per sequence, from the
-# ncu capture summarised in profiles/decode_mma_4bit_b32.md (batch 32: 168.14 MB + 4.20 MB); traffic is
+# ncu capture summarised in profiles/decode_mma_4bit_b32.md (batch 32: 168.20 MB + 4.91 MB); traffic is
 # proportional to the batch, so a batch-64 launch is twice the captured one.
-NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_139_776 + 4_198_656) / 32
+NCU_DRAM_BYTES_PER_SEQ_4BIT = (168_201_216 + 4_908_800) / 32
 METRIC = ("decode tokens/sec of the KV-cache hot path (append + flush + quantized decode attention, 36 layers, "
           "batch 64/GPU, ctx 4096+128)")
 
@@ -360,7 +360,7 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_DRAM_BYTES_PER_SEQ_4BIT * B if bits == 4 else None, "peak_kind": peak_kind, "kernel": "decode_mma_kernel + combine_tiles_kernel",
+                     "traffic": NCU_DRAM_BYTES_PER_SEQ_4BIT * B if bits == 4 else None, "peak_kind": peak_kind, "kernel": "decode_mma_kernel + combine_tiles_warp_kernel",
                      "bytes_per_launch": abytes, "us_per_launch": attn_us},
         "clocks": clocks,
         "parity_check": parity,
