@@ -81,3 +81,39 @@ def test_long_context_131k(oracle, bits, group):
     got = decode_attention(layer, q, 128 ** -0.5, out_dtype=torch.float32)
     err = (got[b0:b0 + 1, :, 4 * h0:4 * h0 + 4].cpu() - want).abs().max().item()
     assert err <= TOL, err
+
+
+@pytest.mark.parametrize("bits,gqa", [(4, 4), (2, 2)])
+def test_split_launch_with_mask_and_ragged_window(oracle, bits, gqa):
+    """Enough packed tiles to fill every warp of the machine twice (16 x 8 pairs x 32 groups), so that the
+    tensor-core kernel splits its launch into CTAs for packed tiles and CTAs for residual tiles; a residual window
+    of 150 tokens (a ragged last tile), a left-padding mask and a mask over packed and residual tokens.  Sequences
+    0, 7 and 15 are checked against the oracle, as normalised output and as the merged (m, l, acc) triple."""
+    import muzero_b200 as mz
+    from muzero_b200.cache.attention import decode_attention, decode_attention_partial_packed
+    B, KVH, S = 16, 8, 2048 + 150
+    H = KVH * gqa
+    rows = [0, 7, 15]
+    k, v, q, kc, vc, qc = _gpu_batch_with_known_rows(oracle, B, KVH, S, H, rows, seed=2200 + bits)
+    layer = mz.MuZeroCacheLayer(mz.MuZeroConfig(bits=bits, q_group_size=64, residual_length=128, alpha_key=2.0, alpha_value=2.0))
+    layer.update(k[:, :, :2048 + 128].contiguous(), v[:, :, :2048 + 128].contiguous(), {"materialize_full_kv": False})
+    for t in range(2048 + 128, S):
+        layer.update(k[:, :, t:t + 1], v[:, :, t:t + 1], {"materialize_full_kv": False})
+    assert layer._key_group_count == 32 and layer.keys.shape[2] == 150
+    mask = torch.zeros(B, 1, 1, S)
+    mask[0, ..., :200] = torch.finfo(torch.bfloat16).min           # left padding
+    mask[7, ..., 1990:2100] = -4.0                                  # across the packed / residual boundary
+    mask[15, ..., S - 9:] = torch.finfo(torch.bfloat16).min        # the ragged last residual tile
+    got = decode_attention(layer, q, 128 ** -0.5, mask.cuda(), out_dtype=torch.float32)
+    rec = decode_attention_partial_packed(layer, q, 128 ** -0.5, mask.cuda())        # [B, H, D + 2] = acc, m, l
+    for i, r in enumerate(rows):
+        ref = oracle.OracleCacheLayer(bits=bits, group=64, residual=128, alpha_key=2.0, alpha_value=2.0)
+        ref.append(kc[i:i + 1, :, :2048 + 128].contiguous(), vc[i:i + 1, :, :2048 + 128].contiguous())
+        for t in range(2048 + 128, S):
+            ref.append(kc[i:i + 1, :, t:t + 1].contiguous(), vc[i:i + 1, :, t:t + 1].contiguous())
+        want = oracle.decode_attention_oracle(qc[i:i + 1], ref, 128 ** -0.5, gqa, mask=mask[r:r + 1], compute_dtype=torch.float32)
+        err = (got[r:r + 1].cpu() - want).abs().max().item()
+        assert err <= TOL, (r, err)
+        pr = rec[r].cpu()
+        from_triple = (pr[:, :128] / pr[:, 129:130]).view(1, 1, H, 128)
+        assert (from_triple - want).abs().max().item() <= TOL, r
