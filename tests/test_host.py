@@ -156,3 +156,25 @@ def test_tile_partition_matches_bruteforce(tmp_path):
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, run.stdout
     assert "BAD" not in run.stdout and run.stdout.count(": ok") == 12
+
+
+def test_prefill_deferral_rules(monkeypatch):
+    """Which prompt blocks stay dense until the first decode step (host logic only).  Reference:
+    muzero/integrations/transformers_patch.py:546-555 defers every block under generate();
+    benchmarks/bench_throughput.py:244-279 quantizes chunk by chunk when it prefills in chunks."""
+    import muzero_b200 as mz
+    from muzero_b200.integrations.transformers_patch import MuZeroCache
+    cfg = mz.MuZeroConfig(bits=4, q_group_size=64, residual_length=128)
+    monkeypatch.delenv("MUZERO_QUANTIZE_PREFILL_CHUNKS", raising=False)
+    cache = MuZeroCache(cfg)
+    assert cache.prefill_block_defers(0) is False            # no deferral asked for
+    cache.defer_prefill_quantization = True
+    cache.single_shot_prefill = True
+    assert cache.prefill_block_defers(0) is False            # the whole prompt in one block: quantized in its own update
+    cache.single_shot_prefill = False
+    assert cache.prefill_block_defers(0) is True             # chunked prefill keeps the reference's deferral ...
+    monkeypatch.setenv("MUZERO_QUANTIZE_PREFILL_CHUNKS", "1")
+    chunked = MuZeroCache(cfg)
+    chunked.defer_prefill_quantization = True
+    chunked.single_shot_prefill = False
+    assert chunked.prefill_block_defers(0) is False          # ... unless chunks are to be quantized as they arrive
